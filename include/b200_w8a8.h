@@ -1,0 +1,136 @@
+/* C ABI of the B200 (sm_100a) W8A8 linear path.
+ *
+ * Every entry point takes plain pointers and sizes.  Unless stated otherwise pointers are
+ * DEVICE pointers owned by the caller, work is enqueued asynchronously on `stream`
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream, B200_STREAM_PER_THREAD
+ * = the per-thread default stream the reference is compiled for), and the return value
+ * follows the reference's operator convention (src/world_cuda_ops.cu:28-42): 0 = success,
+ * 1 = failure with a message on stderr (also kept for b200_w8a8_last_error).  Nothing here
+ * throws, aborts, or falls back to a CPU path.
+ *
+ * Each declaration names the reference interface it stands in for, as
+ * path-in-reference:line.
+ */
+#ifndef B200_W8A8_H
+#define B200_W8A8_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_W8A8_ABI_VERSION 1
+
+/* element types of activations / outputs */
+#define B200_DT_F32 0
+#define B200_DT_F16 1
+#define B200_DT_BF16 2
+#define B200_DT_S32 3
+
+/* epilogue activations */
+#define B200_ACT_NONE 0
+#define B200_ACT_SILU 1
+#define B200_ACT_GELU_TANH 2
+
+/* int8 weight layouts.  ROW_MAJOR is the reference's int8[N,K] (src/world_cuda.cu:153-222).
+ * SLAB128 stores, for each 128-byte slab of K, all N rows contiguously: [K/128][N][128];
+ * a GEMM tile of any height is then one contiguous block of HBM.  Needs K % 128 == 0. */
+#define B200_W_ROW_MAJOR 0
+#define B200_W_SLAB128 1
+
+#define B200_STREAM_PER_THREAD ((void *)0x2)
+
+int b200_w8a8_abi_version(void);
+/* Last failure message of the calling thread ("" if none). */
+const char *b200_w8a8_last_error(void);
+/* Synchronises the current device and reports the status word GEMM kernels leave when one
+ * of their bounded waits ran out (0 = healthy; see KernelStatus in csrc/common.cuh).
+ * The reference has no counterpart: its kernels have no device-side waits. */
+int b200_w8a8_poll_status(int *status_out);
+
+/* ---- activation quantizers ------------------------------------------------------- */
+
+/* Per-row symmetric absmax int8 of rows of x (element type x_dtype, row stride ldx
+ * elements): scales[r] = amax > 0 ? amax/127 : 1, q = clamp(rne(x/scale), -127, 127).
+ * Stands in for wm_cuda_quantize_rows_f32_i8 (src/world_cuda_ops.cuh:20-21; kernel
+ * src/world_cuda_ops.cu:94-125), widened to fp16/bf16 inputs and strided rows. */
+int b200_w8a8_quantize_rows(const void *x, int x_dtype, int64_t ldx, int8_t *q, int64_t ldq, float *scales,
+                            int rows, int cols, void *stream);
+
+/* RMSNorm (eps) * vec_scale + vec_bias, then the quantizer above, in one pass.
+ * vec_scale and vec_bias are nullable.  scale_is_mod = 1 multiplies by (1 + vec_scale[c])
+ * as the reference's AdaRMSNorm does; 0 multiplies by vec_scale[c] (a plain gamma).
+ * Stands in for wm_cuda_rms_norm_quantize_rows_i8 (src/world_cuda_ops.cuh:22-30; kernel
+ * src/world_cuda_ops.cu:129-182). */
+int b200_w8a8_rms_norm_quantize_rows(const void *x, int x_dtype, int64_t ldx, const float *vec_scale,
+                                     int scale_is_mod, const float *vec_bias, int8_t *q, int64_t ldq,
+                                     float *scales, int rows, int cols, float eps, void *stream);
+
+/* v = act(float(acc) * in_row_scales[r] * w_scales[c] (+ bias[c])), then the quantizer.
+ * out_row_scales may alias in_row_scales (the reference's callers do that).
+ * Stands in for wm_cuda_dequant_silu_quantize_rows_i8 (src/world_cuda_ops.cuh:31-39;
+ * kernel src/world_cuda_ops.cu:187-227); act selects SiLU (the reference) or GELU(tanh). */
+int b200_w8a8_dequant_act_quantize_rows(const int32_t *acc, int64_t ldacc, const float *in_row_scales,
+                                        const float *w_scales, const float *bias, int act, int8_t *q, int64_t ldq,
+                                        float *out_row_scales, int rows, int cols, void *stream);
+
+/* out = residual + float(acc) * row_scales[r] * col_scales[c] * (gate ? gate[c] : 1).
+ * residual (nullable) has element type res_dtype, out has out_dtype; both dense [rows, cols].
+ * Stands in for wm_cuda_dequant_gated_residual_f32 and wm_cuda_dequant_add_residual_f32
+ * (src/world_cuda_ops.cuh:40-56; kernels src/world_cuda_ops.cu:229-262). */
+int b200_w8a8_dequant_residual(const int32_t *acc, const float *row_scales, const float *col_scales,
+                               const void *residual, int res_dtype, const float *gate, void *out, int out_dtype,
+                               int rows, int cols, void *stream);
+
+/* Dequantizes a QKV accumulator and applies per-head RMSNorm + 3-axis RoPE to Q and K;
+ * writes head-major fp32 q[Hq,T,d], k[Hkv,T,d], v[Hkv,T,d].
+ * Stands in for wm_cuda_qkv_fused_rms_rope_i32_dequant (src/world_cuda_ops.cuh:120-138;
+ * kernel src/world_cuda_ops.cu:1229-1305). */
+int b200_w8a8_qkv_rms_rope_dequant(const int32_t *qkv_acc, const float *row_scales, const float *weight_scales,
+                                   float *q, float *k, float *v, const int64_t *x_pos, const int64_t *y_pos,
+                                   const int64_t *t_pos, const float *xy, const float *inv_t, int tokens,
+                                   int n_heads, int n_kv_heads, int d_head, int width, int height, float eps,
+                                   void *stream);
+
+/* ---- int8 GEMM and fused linears -------------------------------------------------- */
+
+/* acc[m,n] = sum_k x[m,k] * w[n,k], exact int32.  x is row-major [M,K]; w is row-major
+ * [N,K] (w_layout ROW_MAJOR) or SLAB128.  Needs K % 32 == 0 like the reference, and
+ * 16-byte aligned x / w.  Stand in for wm_cuda_gemm_i8_i32_can_implement and
+ * wm_cuda_gemm_i8_i32 (src/world_cuda_ops.cuh:315-328; src/world_cuda_ops.cu:550-599). */
+int b200_w8a8_gemm_i8_i32_can_implement(const int8_t *x_i8, const int8_t *w_i8, int w_layout,
+                                        const int32_t *acc_i32, int m, int k, int n);
+int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, int32_t *acc_i32, int m, int k,
+                          int n, void *stream);
+
+/* One fused linear: y = store( residual + gate * act( acc * x_scales[r] * w_scales[c] + bias[c] ) )
+ * with bias / gate / residual nullable, y and residual of type y_dtype (fp16, bf16 or fp32)
+ * with row strides ldy / ldr.  It replaces the reference's three-call sequence
+ * quantized GEMM -> int32 scratch -> dequant kernel (e.g. src/world_cuda.cu:2066-2096)
+ * by a GEMM whose epilogue reads the accumulator straight from tensor memory.
+ * workspace: b200_w8a8_linear_workspace_size(m,k,n) bytes of device scratch (may be
+ * NULL when that size is 0). */
+size_t b200_w8a8_linear_workspace_size(int m, int k, int n);
+int b200_w8a8_linear(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                     const float *w_scales, const float *bias, const float *gate, const void *residual,
+                     int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
+                     void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- weights (HOST pointers) ------------------------------------------------------ */
+
+/* Per-output-channel symmetric int8 quantization of host fp32 w[N,K] into `layout`,
+ * using `threads` host threads (<= 0: all cores).  Rejects non-finite weights.
+ * packed_host needs b200_w8a8_packed_weight_bytes(n,k,layout) bytes, scales_host n floats.
+ * Stands in for copy_f32_to_i8_per_output_device (src/world_cuda.cu:153-222) minus the
+ * upload, which stays with the caller. */
+size_t b200_w8a8_packed_weight_bytes(int n, int k, int layout);
+int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
+                               float *scales_host, int threads);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_W8A8_H */

@@ -1,0 +1,199 @@
+"""Python access to libb200_w8a8.so (the sm_100a W8A8 linear path) through its C ABI.
+
+This is harness code for tests and benchmarks: it loads the shared library with ctypes,
+declares the prototypes of include/b200_w8a8.h and offers thin helpers that pass
+`torch.Tensor.data_ptr()` values.  There is no fallback of any kind: if the library has
+not been built, importing `lib()` raises, and every wrapper raises `W8A8Error` when the C
+function returns non-zero.
+
+The directory name contains a dot, so it is not importable by name; load it with
+`importlib.util.spec_from_file_location("worldmodel_cu_b200", ".../__init__.py")`
+(see `__graft_entry__.load_package`).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p, POINTER
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libb200_w8a8.so"
+
+DT_F32, DT_F16, DT_BF16, DT_S32 = 0, 1, 2, 3
+ACT_NONE, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
+W_ROW_MAJOR, W_SLAB128 = 0, 1
+
+
+class W8A8Error(RuntimeError):
+    pass
+
+
+_PROTOTYPES = {
+    "b200_w8a8_abi_version": (c_int, []),
+    "b200_w8a8_last_error": (c_char_p, []),
+    "b200_w8a8_poll_status": (c_int, [POINTER(c_int)]),
+    "b200_w8a8_quantize_rows": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
+    "b200_w8a8_rms_norm_quantize_rows": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                                                 c_int64, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "b200_w8a8_dequant_act_quantize_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                    c_int64, c_void_p, c_int, c_int, c_void_p]),
+    "b200_w8a8_dequant_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                           c_int, c_int, c_void_p]),
+    "b200_w8a8_qkv_rms_rope_dequant": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_float, c_void_p]),
+    "b200_w8a8_gemm_i8_i32_can_implement": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int]),
+    "b200_w8a8_gemm_i8_i32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_w8a8_linear_workspace_size": (c_size_t, [c_int, c_int, c_int]),
+    "b200_w8a8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                 c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_w8a8_packed_weight_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "b200_w8a8_pack_weight_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
+}
+
+_lib = None
+
+
+def exported_symbols():
+    """Names this module expects the library to export (every declaration of the C header)."""
+    return sorted(_PROTOTYPES)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise W8A8Error(f"{LIB_PATH} is missing: run `python worldmodel.cu_b200/build.py` (needs nvcc); "
+                            "there is no fallback path")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _PROTOTYPES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        msg = lib().b200_w8a8_last_error()
+        raise W8A8Error(f"{what} failed: {msg.decode() if msg else '?'}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t) -> int:
+    import torch
+    return {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.int32: DT_S32}[t.dtype]
+
+
+def poll_status() -> int:
+    st = c_int(0)
+    _check(lib().b200_w8a8_poll_status(ctypes.byref(st)), "poll_status")
+    return st.value
+
+
+# ------------------------------------------------------------------ operators on CUDA tensors
+def quantize_rows(x, cols=None):
+    """x: [rows, >=cols] CUDA tensor (fp32/fp16/bf16), last dim contiguous.  Returns (q int8, scales)."""
+    import torch
+    rows = x.shape[0]
+    cols = x.shape[1] if cols is None else cols
+    q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
+    s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(lib().b200_w8a8_quantize_rows(_ptr(x), _dt(x), x.stride(0), _ptr(q), cols, _ptr(s), rows, cols, _stream()),
+           "quantize_rows")
+    return q, s
+
+
+def rms_norm_quantize_rows(x, vec_scale=None, bias=None, eps=1e-6, scale_is_mod=True):
+    import torch
+    rows, cols = x.shape
+    q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
+    s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(lib().b200_w8a8_rms_norm_quantize_rows(_ptr(x), _dt(x), x.stride(0), _ptr(vec_scale), int(scale_is_mod),
+                                                  _ptr(bias), _ptr(q), cols, _ptr(s), rows, cols, eps, _stream()),
+           "rms_norm_quantize_rows")
+    return q, s
+
+
+def dequant_act_quantize_rows(acc, in_row_scales, w_scales, bias=None, act=ACT_SILU, out_row_scales=None):
+    import torch
+    rows, cols = acc.shape
+    q = torch.empty(rows, cols, dtype=torch.int8, device=acc.device)
+    s = torch.empty(rows, dtype=torch.float32, device=acc.device) if out_row_scales is None else out_row_scales
+    _check(lib().b200_w8a8_dequant_act_quantize_rows(_ptr(acc), acc.stride(0), _ptr(in_row_scales), _ptr(w_scales),
+                                                     _ptr(bias), act, _ptr(q), cols, _ptr(s), rows, cols, _stream()),
+           "dequant_act_quantize_rows")
+    return q, s
+
+
+def dequant_residual(acc, row_scales, col_scales, residual=None, gate=None, out_dtype=None):
+    import torch
+    rows, cols = acc.shape
+    out_dtype = out_dtype or (residual.dtype if residual is not None else torch.float32)
+    out = torch.empty(rows, cols, dtype=out_dtype, device=acc.device)
+    _check(lib().b200_w8a8_dequant_residual(_ptr(acc), _ptr(row_scales), _ptr(col_scales), _ptr(residual),
+                                            _dt(residual) if residual is not None else _dt(out), _ptr(gate),
+                                            _ptr(out), _dt(out), rows, cols, _stream()), "dequant_residual")
+    return out
+
+
+def qkv_rms_rope_dequant(acc, row_scales, w_scales, x_pos, y_pos, t_pos, xy, inv_t, n_heads, n_kv_heads, d_head,
+                         width, height, eps):
+    import torch
+    T = acc.shape[0]
+    q = torch.empty(n_heads, T, d_head, dtype=torch.float32, device=acc.device)
+    k = torch.empty(n_kv_heads, T, d_head, dtype=torch.float32, device=acc.device)
+    v = torch.empty(n_kv_heads, T, d_head, dtype=torch.float32, device=acc.device)
+    _check(lib().b200_w8a8_qkv_rms_rope_dequant(_ptr(acc), _ptr(row_scales), _ptr(w_scales), _ptr(q), _ptr(k), _ptr(v),
+                                                _ptr(x_pos), _ptr(y_pos), _ptr(t_pos), _ptr(xy), _ptr(inv_t), T,
+                                                n_heads, n_kv_heads, d_head, width, height, eps, _stream()),
+           "qkv_rms_rope_dequant")
+    return q, k, v
+
+
+def gemm_i8_i32(x_i8, w_i8, n=None, w_layout=W_ROW_MAJOR):
+    import torch
+    m, k = x_i8.shape
+    n = w_i8.shape[0] if n is None else n
+    acc = torch.empty(m, n, dtype=torch.int32, device=x_i8.device)
+    _check(lib().b200_w8a8_gemm_i8_i32(_ptr(x_i8), _ptr(w_i8), w_layout, _ptr(acc), m, k, n, _stream()), "gemm_i8_i32")
+    return acc
+
+
+def linear(x_i8, x_scales, w_i8, w_scales, n=None, w_layout=W_ROW_MAJOR, bias=None, gate=None, residual=None,
+           act=ACT_NONE, out_dtype=None, out=None):
+    import torch
+    m, k = x_i8.shape
+    n = w_scales.shape[0] if n is None else n
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype or torch.float16, device=x_i8.device)
+    ws_bytes = lib().b200_w8a8_linear_workspace_size(m, k, n)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x_i8.device) if ws_bytes else None
+    _check(lib().b200_w8a8_linear(_ptr(x_i8), _ptr(x_scales), _ptr(w_i8), w_layout, _ptr(w_scales), _ptr(bias),
+                                  _ptr(gate), _ptr(residual), residual.stride(0) if residual is not None else 0,
+                                  _ptr(out), _dt(out), out.stride(0), m, k, n, act, _ptr(ws), ws_bytes, _stream()),
+           "linear")
+    return out
+
+
+def pack_weight(w_f32_cpu, layout=W_SLAB128, threads=0):
+    """Host fp32 [N,K] -> (int8 packed CPU tensor [N*K], fp32 scales [N])."""
+    import torch
+    w = w_f32_cpu.contiguous().to(torch.float32)
+    n, k = w.shape
+    nbytes = lib().b200_w8a8_packed_weight_bytes(n, k, layout)
+    if nbytes == 0:
+        raise W8A8Error(f"layout {layout} cannot hold N={n} K={k}")
+    packed = torch.empty(nbytes, dtype=torch.int8)
+    scales = torch.empty(n, dtype=torch.float32)
+    _check(lib().b200_w8a8_pack_weight_host(w.data_ptr(), n, k, layout, packed.data_ptr(), scales.data_ptr(), threads),
+           "pack_weight_host")
+    return packed, scales

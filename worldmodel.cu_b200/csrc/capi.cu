@@ -1,0 +1,121 @@
+// extern "C" shells over the internal C++ interface, plus the error plumbing.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "w8a8_internal.h"
+
+namespace b200 {
+
+namespace {
+thread_local char t_error[512] = "";
+}
+
+int fail(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+    fprintf(stderr, "b200_w8a8: %s\n", t_error);
+    return 1;
+}
+
+int check_launch(const char *what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();  // clear a non-sticky launch error so the next call starts clean
+        return fail("CUDA error after launching %s: %s", what, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+const char *last_error_message() { return t_error; }
+
+static inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_w8a8_abi_version(void) { return B200_W8A8_ABI_VERSION; }
+const char *b200_w8a8_last_error(void) { return last_error_message(); }
+int b200_w8a8_poll_status(int *status_out) { return gemm_poll_status(status_out); }
+
+int b200_w8a8_quantize_rows(const void *x, int x_dtype, int64_t ldx, int8_t *q, int64_t ldq, float *scales,
+                            int rows, int cols, void *stream) {
+    return quantize_rows(x, x_dtype, ldx, q, ldq, scales, rows, cols, as_stream(stream));
+}
+
+int b200_w8a8_rms_norm_quantize_rows(const void *x, int x_dtype, int64_t ldx, const float *vec_scale,
+                                     int scale_is_mod, const float *vec_bias, int8_t *q, int64_t ldq,
+                                     float *scales, int rows, int cols, float eps, void *stream) {
+    return rms_norm_quantize_rows(x, x_dtype, ldx, vec_scale, scale_is_mod, vec_bias, q, ldq, scales, rows, cols,
+                                  eps, as_stream(stream));
+}
+
+int b200_w8a8_dequant_act_quantize_rows(const int32_t *acc, int64_t ldacc, const float *in_row_scales,
+                                        const float *w_scales, const float *bias, int act, int8_t *q, int64_t ldq,
+                                        float *out_row_scales, int rows, int cols, void *stream) {
+    return dequant_act_quantize_rows(acc, ldacc, in_row_scales, w_scales, bias, act, q, ldq, out_row_scales, rows,
+                                     cols, as_stream(stream));
+}
+
+int b200_w8a8_dequant_residual(const int32_t *acc, const float *row_scales, const float *col_scales,
+                               const void *residual, int res_dtype, const float *gate, void *out, int out_dtype,
+                               int rows, int cols, void *stream) {
+    return dequant_residual(acc, row_scales, col_scales, residual, res_dtype, gate, out, out_dtype, rows, cols,
+                            as_stream(stream));
+}
+
+int b200_w8a8_qkv_rms_rope_dequant(const int32_t *qkv_acc, const float *row_scales, const float *weight_scales,
+                                   float *q, float *k, float *v, const int64_t *x_pos, const int64_t *y_pos,
+                                   const int64_t *t_pos, const float *xy, const float *inv_t, int tokens,
+                                   int n_heads, int n_kv_heads, int d_head, int width, int height, float eps,
+                                   void *stream) {
+    return qkv_rms_rope_dequant(qkv_acc, row_scales, weight_scales, q, k, v, x_pos, y_pos, t_pos, xy, inv_t, tokens,
+                                n_heads, n_kv_heads, d_head, width, height, eps, as_stream(stream));
+}
+
+static LinearArgs raw_gemm_args(const int8_t *x, const int8_t *w, int w_layout, const int32_t *acc, int m, int k,
+                                int n) {
+    LinearArgs a{};
+    a.x = x; a.w = w; a.w_layout = w_layout; a.m = m; a.k = k; a.n = n;
+    a.out = const_cast<int32_t *>(acc); a.ldo = n; a.out_dtype = B200_DT_S32;
+    return a;
+}
+
+int b200_w8a8_gemm_i8_i32_can_implement(const int8_t *x_i8, const int8_t *w_i8, int w_layout,
+                                        const int32_t *acc_i32, int m, int k, int n) {
+    return gemm_can_implement(raw_gemm_args(x_i8, w_i8, w_layout, acc_i32, m, k, n), true);
+}
+
+int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, int32_t *acc_i32, int m, int k,
+                          int n, void *stream) {
+    return gemm_launch(raw_gemm_args(x_i8, w_i8, w_layout, acc_i32, m, k, n), nullptr, 0, as_stream(stream));
+}
+
+size_t b200_w8a8_linear_workspace_size(int m, int k, int n) { return gemm_workspace_size(m, k, n); }
+
+int b200_w8a8_linear(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                     const float *w_scales, const float *bias, const float *gate, const void *residual,
+                     int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
+                     void *workspace, size_t workspace_bytes, void *stream) {
+    if (y_dtype == B200_DT_S32) return fail("b200_w8a8_linear writes fp16, bf16 or fp32; use gemm_i8_i32 for int32");
+    LinearArgs a{};
+    a.x = x_i8; a.w = w_i8; a.w_layout = w_layout; a.m = m; a.k = k; a.n = n;
+    a.row_scales = x_scales; a.col_scales = w_scales; a.bias = bias; a.gate = gate;
+    a.residual = residual; a.ldr = residual ? ldr : ldy; a.act = act;
+    a.out = y; a.ldo = ldy; a.out_dtype = y_dtype;
+    return gemm_launch(a, workspace, workspace_bytes, as_stream(stream));
+}
+
+size_t b200_w8a8_packed_weight_bytes(int n, int k, int layout) { return packed_weight_bytes(n, k, layout); }
+
+int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
+                               float *scales_host, int threads) {
+    return pack_weight_host(w_host, n, k, layout, packed_host, scales_host, threads);
+}
+
+}  // extern "C"

@@ -1,0 +1,200 @@
+// Shared device helpers for the sm_100a W8A8 kernels: mbarrier / TMA / tcgen05 wrappers
+// around inline PTX, bounded waits, and the fp32 arithmetic that must stay un-contracted
+// so results agree bit-for-bit with a CPU evaluation of the same formulas.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// Status words a kernel can leave in the device-side status slot (0 = healthy).
+enum KernelStatus : int {
+    KS_OK = 0,
+    KS_TIMEOUT_SMEM_EMPTY = 101,  // producer waited too long for a free pipeline stage
+    KS_TIMEOUT_SMEM_FULL = 102,   // MMA issuer waited too long for an operand stage
+    KS_TIMEOUT_TMEM_EMPTY = 103,  // MMA issuer waited too long for a drained accumulator
+    KS_TIMEOUT_TMEM_FULL = 104,   // epilogue waited too long for a finished accumulator
+};
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---------------------------------------------------------------- mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for `parity` of `bar` with a time limit.  On expiry it raises the CTA-wide abort
+// flag, records `code` in the device status slot and returns false; it also returns false
+// as soon as another role of the CTA has raised the abort flag.  Nothing ever spins forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                                  int *status_slot, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if (((++spins) & 0xFFu) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status_slot) atomicCAS(status_slot, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------- TMA (tile mode, 3-D, no cluster fan-out)
+__device__ __forceinline__ void tma_prefetch_desc(const void *tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const void *tmap, uint64_t *bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// ---------------------------------------------------------------- tcgen05 / TMEM
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, signed 8-bit operands, 32-bit integer accumulators.
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base+t).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 64-bit shared-memory operand descriptor for a K-major tile whose rows are 128 bytes and
+// were written by TMA with the 128-byte swizzle: eight-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_smem_desc_k128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);  // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                       // descriptor version for this architecture
+    d |= (uint64_t)2 << 61;                       // 128-byte swizzle
+    return d;
+}
+// 32-bit instruction descriptor: s8 x s8 -> s32, both operands K-major, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc_i8(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- exact fp32 pieces
+// Symmetric absmax scale and code, IEEE division on both (never a reciprocal multiply).
+__device__ __forceinline__ float absmax_to_scale(float amax) {
+    return amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+}
+__device__ __forceinline__ int quantize_code(float v, float scale) {
+    int q = __float2int_rn(__fdiv_rn(v, scale));
+    return max(-127, min(127, q));
+}
+__device__ __forceinline__ float dequant_acc(int acc, float row_scale, float col_scale) {
+    return __fmul_rn(__fmul_rn((float)acc, row_scale), col_scale);
+}
+__device__ __forceinline__ float act_silu(float v) {
+    return __fdiv_rn(v, __fadd_rn(1.0f, expf(-v)));
+}
+// 0.5 * v * (1 + tanh(sqrt(2/pi) * (v + 0.044715 v^3))), operation order of the usual
+// fp32 reference evaluation, no fused multiply-adds.
+__device__ __forceinline__ float act_gelu_tanh(float v) {
+    const float kBeta = 0.7978845608028654f;
+    const float kKappa = 0.044715f;
+    float v3 = __fmul_rn(__fmul_rn(v, v), v);
+    float inner = __fmul_rn(kBeta, __fadd_rn(v, __fmul_rn(kKappa, v3)));
+    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner)));
+}
+template <int ACT>
+__device__ __forceinline__ float apply_act(float v) {
+    if (ACT == 1) return act_silu(v);
+    if (ACT == 2) return act_gelu_tanh(v);
+    return v;
+}
+__device__ __forceinline__ float apply_act_rt(float v, int act) {
+    if (act == 1) return act_silu(v);
+    if (act == 2) return act_gelu_tanh(v);
+    return v;
+}
+
+}  // namespace b200

@@ -1,0 +1,354 @@
+// Per-token activation quantizers: plain absmax -> A8, fused (Ada)RMSNorm -> A8, and
+// dequant -> bias -> activation -> A8 of an int32 accumulator.
+//
+// They replace the reference's one-CTA-per-row, scalar, three-pass kernels
+// (src/world_cuda_ops.cu:94-125, 129-182, 187-227).  Here a row is owned by a group of
+// G threads (one warp, or the whole 256-thread CTA), is read from global memory exactly
+// once with 16/32-byte vector loads, lives in registers across the reductions, and is
+// written back as packed 8-byte code vectors.  Reductions are warp shuffles (plus one
+// shared-memory hop when G spans several warps).  All of these kernels are bound by HBM
+// traffic: bytes in + 1 byte per element out.
+#include "common.cuh"
+#include "w8a8_internal.h"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxVec = 8;  // 8-element vectors held per thread
+
+enum Mode { MODE_PLAIN = 0, MODE_RMS = 1, MODE_DEQ_ACT = 2 };
+
+struct QuantArgs {
+    const void *x;          // input rows (fp32 / fp16 / bf16 / int32 accumulators)
+    long long ldx;          // input row stride in elements
+    int8_t *q;              // output codes
+    long long ldq;          // output row stride in elements
+    float *scales;          // output per-row scales
+    int rows, cols;
+    // MODE_RMS
+    const float *vec_scale;  // gamma or mod_scale, nullable
+    const float *vec_bias;   // nullable
+    int scale_is_mod;        // 1: multiply by (1 + vec_scale[col])
+    float eps;
+    // MODE_DEQ_ACT
+    const float *in_row_scales;
+    const float *col_scales;
+    int act;
+};
+
+template <typename T>
+struct Load8;
+template <>
+struct Load8<float> {
+    static __device__ __forceinline__ void run(const void *p, float (&v)[8]) {
+        const float4 *s = reinterpret_cast<const float4 *>(p);
+        float4 a = s[0], b = s[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ float one(const void *p, long long i) {
+        return reinterpret_cast<const float *>(p)[i];
+    }
+};
+template <>
+struct Load8<int32_t> {
+    static __device__ __forceinline__ void run(const void *p, float (&v)[8]) {
+        const int4 *s = reinterpret_cast<const int4 *>(p);
+        int4 a = s[0], b = s[1];
+        v[0] = (float)a.x; v[1] = (float)a.y; v[2] = (float)a.z; v[3] = (float)a.w;
+        v[4] = (float)b.x; v[5] = (float)b.y; v[6] = (float)b.z; v[7] = (float)b.w;
+    }
+    static __device__ __forceinline__ float one(const void *p, long long i) {
+        return (float)reinterpret_cast<const int32_t *>(p)[i];
+    }
+};
+template <>
+struct Load8<__half> {
+    static __device__ __forceinline__ void run(const void *p, float (&v)[8]) {
+        uint4 raw = *reinterpret_cast<const uint4 *>(p);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ float one(const void *p, long long i) {
+        return __half2float(reinterpret_cast<const __half *>(p)[i]);
+    }
+};
+template <>
+struct Load8<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(const void *p, float (&v)[8]) {
+        uint4 raw = *reinterpret_cast<const uint4 *>(p);
+        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ float one(const void *p, long long i) {
+        return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+    }
+};
+
+__device__ __forceinline__ void load8f(const float *p, float (&v)[8]) { Load8<float>::run(p, v); }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Reduction over the G threads that own one row.  For G == 32 it is a pure shuffle; for
+// G == kThreads every warp of the CTA posts its partial to shared memory.
+template <int G>
+__device__ __forceinline__ float group_max(float v, float *red) {
+    v = warp_max(v);
+    if (G == 32) return v;
+    __syncthreads();  // protect `red` from the previous use
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) r = fmaxf(r, red[i]);
+    return r;
+}
+template <int G>
+__device__ __forceinline__ double group_sum(double v, double *red) {
+    v = warp_sum(v);
+    if (G == 32) return v;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double r = red[0];
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) r += red[i];
+    return r;
+}
+
+// The transform each mode applies to a loaded vector of 8 elements at column `col`.
+template <int MODE>
+__device__ __forceinline__ void transform8(float (&v)[8], int col, const QuantArgs &a, float row_factor) {
+    if (MODE == MODE_RMS) {
+        float s[8], b[8];
+        if (a.vec_scale) load8f(a.vec_scale + col, s);
+        if (a.vec_bias) load8f(a.vec_bias + col, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float t = __fmul_rn(v[i], row_factor);
+            if (a.vec_scale) t = __fmul_rn(t, a.scale_is_mod ? __fadd_rn(1.0f, s[i]) : s[i]);
+            if (a.vec_bias) t = __fadd_rn(t, b[i]);
+            v[i] = t;
+        }
+    } else if (MODE == MODE_DEQ_ACT) {
+        float s[8], b[8];
+        load8f(a.col_scales + col, s);
+        if (a.vec_bias) load8f(a.vec_bias + col, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float t = __fmul_rn(__fmul_rn(v[i], row_factor), s[i]);
+            if (a.vec_bias) t = __fadd_rn(t, b[i]);
+            v[i] = apply_act_rt(t, a.act);
+        }
+    }
+}
+
+// Fast path: cols % 8 == 0, 16-byte aligned rows, cols <= G * 8 * kMaxVec.
+template <typename T, int MODE, int G>
+__global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
+    __shared__ float red_f[kThreads / 32];
+    __shared__ double red_d[kThreads / 32];
+    constexpr int kRowsPerCta = kThreads / G;
+    const int gid = threadIdx.x / G;
+    const int gl = threadIdx.x % G;
+    const int row = blockIdx.x * kRowsPerCta + gid;
+    const bool live = row < a.rows;
+    const int nvec = a.cols >> 3;
+
+    const T *xrow = reinterpret_cast<const T *>(a.x) + (long long)row * a.ldx;
+    float v[kMaxVec][8];
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        int vi = gl + j * G;
+        if (live && vi < nvec) {
+            Load8<T>::run(xrow + 8 * vi, v[j]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[j][i] = 0.0f;
+        }
+    }
+
+    float row_factor = 1.0f;
+    if (MODE == MODE_RMS) {
+        double ss = 0.0;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                double d = (double)v[j][i];
+                ss = fma(d, d, ss);
+            }
+        }
+        ss = group_sum<G>(ss, red_d);
+        row_factor = (float)(1.0 / sqrt(ss / (double)a.cols + (double)a.eps));
+    } else if (MODE == MODE_DEQ_ACT) {
+        // read before any store: the output scale vector may alias this one
+        row_factor = live ? a.in_row_scales[row] : 0.0f;
+    }
+
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        int vi = gl + j * G;
+        if (live && vi < nvec) {
+            transform8<MODE>(v[j], 8 * vi, a, row_factor);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+        }
+    }
+    amax = group_max<G>(amax, red_f);
+    const float scale = absmax_to_scale(amax);
+    if (live && gl == 0) a.scales[row] = scale;
+
+    int8_t *qrow = a.q + (long long)row * a.ldq;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        int vi = gl + j * G;
+        if (live && vi < nvec) {
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                lo |= (uint32_t)(quantize_code(v[j][i], scale) & 0xFF) << (8 * i);
+                hi |= (uint32_t)(quantize_code(v[j][i + 4], scale) & 0xFF) << (8 * i);
+            }
+            *reinterpret_cast<uint2 *>(qrow + 8 * vi) = make_uint2(lo, hi);
+        }
+    }
+}
+
+// General path for any width / alignment: one CTA per row, the row is re-read for each
+// pass.  Only odd shapes land here.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kThreads) quant_rows_any_kernel(QuantArgs a) {
+    __shared__ float red_f[kThreads / 32];
+    __shared__ double red_d[kThreads / 32];
+    const int row = blockIdx.x;
+    const T *xrow = reinterpret_cast<const T *>(a.x) + (long long)row * a.ldx;
+
+    float row_factor = 1.0f;
+    if (MODE == MODE_RMS) {
+        double ss = 0.0;
+        for (int c = threadIdx.x; c < a.cols; c += kThreads) {
+            double d = (double)Load8<T>::one(xrow, c);
+            ss = fma(d, d, ss);
+        }
+        ss = group_sum<kThreads>(ss, red_d);
+        row_factor = (float)(1.0 / sqrt(ss / (double)a.cols + (double)a.eps));
+    } else if (MODE == MODE_DEQ_ACT) {
+        row_factor = a.in_row_scales[row];
+    }
+    auto value = [&](int c) -> float {
+        float t = Load8<T>::one(xrow, c);
+        if (MODE == MODE_RMS) {
+            t = __fmul_rn(t, row_factor);
+            if (a.vec_scale) t = __fmul_rn(t, a.scale_is_mod ? __fadd_rn(1.0f, a.vec_scale[c]) : a.vec_scale[c]);
+            if (a.vec_bias) t = __fadd_rn(t, a.vec_bias[c]);
+        } else if (MODE == MODE_DEQ_ACT) {
+            t = __fmul_rn(__fmul_rn(t, row_factor), a.col_scales[c]);
+            if (a.vec_bias) t = __fadd_rn(t, a.vec_bias[c]);
+            t = apply_act_rt(t, a.act);
+        }
+        return t;
+    };
+    float amax = 0.0f;
+    for (int c = threadIdx.x; c < a.cols; c += kThreads) amax = fmaxf(amax, fabsf(value(c)));
+    amax = group_max<kThreads>(amax, red_f);
+    const float scale = absmax_to_scale(amax);
+    __syncthreads();  // every thread has read in_row_scales[row] before it may be overwritten
+    if (threadIdx.x == 0) a.scales[row] = scale;
+    int8_t *qrow = a.q + (long long)row * a.ldq;
+    for (int c = threadIdx.x; c < a.cols; c += kThreads) qrow[c] = (int8_t)quantize_code(value(c), scale);
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T, int MODE>
+int launch_quant(const QuantArgs &a, cudaStream_t stream) {
+    if (a.rows == 0 || a.cols == 0) return 0;
+    const size_t esz = sizeof(T);
+    bool vec_ok = (a.cols % 8 == 0) && aligned16(a.x) && ((a.ldx * esz) % 16 == 0) &&
+                  ((reinterpret_cast<uintptr_t>(a.q) & 7u) == 0) && (a.ldq % 8 == 0) &&
+                  a.cols <= kThreads * 8 * kMaxVec;
+    if (MODE == MODE_RMS) vec_ok = vec_ok && (!a.vec_scale || aligned16(a.vec_scale)) && (!a.vec_bias || aligned16(a.vec_bias));
+    if (MODE == MODE_DEQ_ACT) vec_ok = vec_ok && aligned16(a.col_scales) && (!a.vec_bias || aligned16(a.vec_bias));
+    if (!vec_ok) {
+        quant_rows_any_kernel<T, MODE><<<a.rows, kThreads, 0, stream>>>(a);
+        return check_launch("quant_rows_any");
+    }
+    // A warp per row when there are many rows and the row fits 32 lanes; else a CTA per row.
+    const bool warp_rows = a.cols <= 32 * 8 * kMaxVec && (a.rows >= 4096 || a.cols <= 512);
+    if (warp_rows) {
+        constexpr int kRows = kThreads / 32;
+        quant_rows_vec_kernel<T, MODE, 32><<<(a.rows + kRows - 1) / kRows, kThreads, 0, stream>>>(a);
+    } else {
+        quant_rows_vec_kernel<T, MODE, kThreads><<<a.rows, kThreads, 0, stream>>>(a);
+    }
+    return check_launch("quant_rows_vec");
+}
+
+template <int MODE>
+int dispatch_in_dtype(int in_dtype, const QuantArgs &a, cudaStream_t stream) {
+    switch (in_dtype) {
+        case B200_DT_F32: return launch_quant<float, MODE>(a, stream);
+        case B200_DT_F16: return launch_quant<__half, MODE>(a, stream);
+        case B200_DT_BF16: return launch_quant<__nv_bfloat16, MODE>(a, stream);
+        default: return fail("unsupported activation dtype %d", in_dtype);
+    }
+}
+
+}  // namespace
+
+int quantize_rows(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
+                  int cols, cudaStream_t stream) {
+    if (!x || !q || !scales || rows < 0 || cols < 0 || ldx < cols || ldq < cols)
+        return fail("invalid quantize_rows arguments rows=%d cols=%d", rows, cols);
+    QuantArgs a{};
+    a.x = x; a.ldx = ldx; a.q = q; a.ldq = ldq; a.scales = scales; a.rows = rows; a.cols = cols;
+    return dispatch_in_dtype<MODE_PLAIN>(in_dtype, a, stream);
+}
+
+int rms_norm_quantize_rows(const void *x, int in_dtype, long long ldx, const float *vec_scale, int scale_is_mod,
+                           const float *vec_bias, int8_t *q, long long ldq, float *scales, int rows, int cols,
+                           float eps, cudaStream_t stream) {
+    if (!x || !q || !scales || rows < 0 || cols < 0 || ldx < cols || ldq < cols)
+        return fail("invalid rms_norm_quantize_rows arguments rows=%d cols=%d", rows, cols);
+    QuantArgs a{};
+    a.x = x; a.ldx = ldx; a.q = q; a.ldq = ldq; a.scales = scales; a.rows = rows; a.cols = cols;
+    a.vec_scale = vec_scale; a.vec_bias = vec_bias; a.scale_is_mod = scale_is_mod; a.eps = eps;
+    return dispatch_in_dtype<MODE_RMS>(in_dtype, a, stream);
+}
+
+int dequant_act_quantize_rows(const int32_t *acc, long long ldacc, const float *in_row_scales,
+                              const float *col_scales, const float *bias, int act, int8_t *q, long long ldq,
+                              float *out_row_scales, int rows, int cols, cudaStream_t stream) {
+    if (!acc || !in_row_scales || !col_scales || !q || !out_row_scales || rows < 0 || cols < 0 || ldacc < cols ||
+        ldq < cols || act < 0 || act > 2)
+        return fail("invalid dequant_act_quantize_rows arguments rows=%d cols=%d act=%d", rows, cols, act);
+    QuantArgs a{};
+    a.x = acc; a.ldx = ldacc; a.q = q; a.ldq = ldq; a.scales = out_row_scales; a.rows = rows; a.cols = cols;
+    a.in_row_scales = in_row_scales; a.col_scales = col_scales; a.vec_bias = bias; a.act = act;
+    return launch_quant<int32_t, MODE_DEQ_ACT>(a, stream);
+}
+
+}  // namespace b200

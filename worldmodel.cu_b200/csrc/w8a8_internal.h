@@ -1,0 +1,67 @@
+// Internal C++ interface shared by the translation units of the library.  The exported
+// C ABI (include/b200_w8a8.h) and the reference-named operators are thin shells over this.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/b200_w8a8.h"
+
+namespace b200 {
+
+// Records a message (stderr + thread-local buffer) and returns 1: the reference's
+// operators report failure as `return 1` after printing (src/world_cuda_ops.cu:28-42).
+int fail(const char *fmt, ...);
+// cudaPeekAtLastError after a launch, like the reference's wm_cuda_check_launch
+// (src/world_cuda_ops.cu:2856-2863).
+int check_launch(const char *what);
+const char *last_error_message();
+
+// ---- quant_rows.cu
+int quantize_rows(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
+                  int cols, cudaStream_t stream);
+int rms_norm_quantize_rows(const void *x, int in_dtype, long long ldx, const float *vec_scale, int scale_is_mod,
+                           const float *vec_bias, int8_t *q, long long ldq, float *scales, int rows, int cols,
+                           float eps, cudaStream_t stream);
+int dequant_act_quantize_rows(const int32_t *acc, long long ldacc, const float *in_row_scales,
+                              const float *col_scales, const float *bias, int act, int8_t *q, long long ldq,
+                              float *out_row_scales, int rows, int cols, cudaStream_t stream);
+
+// ---- dequant_ops.cu
+int dequant_residual(const int32_t *acc, const float *row_scales, const float *col_scales, const void *residual,
+                     int res_dtype, const float *gate, void *out, int out_dtype, int rows, int cols,
+                     cudaStream_t stream);
+int qkv_rms_rope_dequant(const int32_t *qkv_acc, const float *row_scales, const float *weight_scales, float *q,
+                         float *k, float *v, const int64_t *x_pos, const int64_t *y_pos, const int64_t *t_pos,
+                         const float *xy, const float *inv_t, int tokens, int n_heads, int n_kv_heads, int d_head,
+                         int width, int height, float eps, cudaStream_t stream);
+
+// ---- gemm_i8_tcgen05.cu
+struct LinearArgs {
+    const int8_t *x;          // A8 codes [m, k], row stride k
+    const int8_t *w;          // W8 codes, row-major [n, k] or slab layout
+    int w_layout;             // B200_W_ROW_MAJOR / B200_W_SLAB128
+    int m, k, n;
+    // epilogue (all nullable except out)
+    const float *row_scales;  // [m]
+    const float *col_scales;  // [n]
+    const float *bias;        // [n]
+    const float *gate;        // [n]
+    const void *residual;     // [m, ldr] in out dtype
+    long long ldr;
+    int act;
+    void *out;                // [m, ldo]
+    long long ldo;
+    int out_dtype;            // B200_DT_S32 means raw accumulators, epilogue inputs ignored
+};
+int gemm_can_implement(const LinearArgs &a, bool verbose);
+int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+size_t gemm_workspace_size(int m, int k, int n);
+int gemm_poll_status(int *status_out);
+
+// ---- pack_weights.cpp
+int pack_weight_host(const float *w, int n, int k, int layout, int8_t *packed, float *scales, int threads);
+size_t packed_weight_bytes(int n, int k, int layout);
+
+}  // namespace b200
