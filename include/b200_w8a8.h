@@ -129,6 +129,43 @@ size_t b200_w8a8_packed_weight_bytes(int n, int k, int layout);
 int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
                                float *scales_host, int threads);
 
+/* ---- the linear stack (host-side driver above the operators) ----------------------- */
+
+/* An opaque object that owns the packed int8 weights of n_layers layers plus activation
+ * scratch on the current device and runs the per-layer operator sequence
+ *   RMSNorm+A8 -> QKV linear -> A8 of the first d_model columns -> out linear + residual ->
+ *   RMSNorm+A8 -> controller linear + residual -> RMSNorm+A8 -> up linear + GELU(tanh) ->
+ *   A8 of the fp32 hidden -> down linear + residual
+ * on 16-bit activations [rows, d_model].  It plays the role of the reference runtime's
+ * weight upload (wm_cuda_copy_world_layers_to_device, src/world_cuda.cu:442-539), shared
+ * W8A8 scratch (src/world_cuda.cu:1311-1317, 1389-1392) and layer loop
+ * (world_cuda_runtime_step_rgb, src/world_cuda.cu:1819-2330) for the linears only.
+ * band_rows > 0 walks the rows in bands of that height (one band through all layers of a
+ * pass before the next band), which keeps a band's intermediates L2-resident.
+ * Returns NULL on failure. */
+void *b200_w8a8_stack_create(int d_model, int n_qkv, int d_hidden, int n_layers, int max_rows, int band_rows,
+                             int act_dtype, float eps);
+void b200_w8a8_stack_destroy(void *stack);
+/* HOST fp32 weights [N,K] (row-major) and gammas of one layer: quantized per output
+ * channel, packed to SLAB128 and uploaded; blocks until the copies are done. */
+int b200_w8a8_stack_set_layer(void *stack, int layer, const float *w_qkv, const float *w_out, const float *w_ctrl,
+                              const float *w_up, const float *w_down, const float *g_attn, const float *g_ctrl,
+                              const float *g_mlp, int threads);
+/* `steps` chained passes over all layers; x_dev is read, y_dev is written, both
+ * [rows, d_model] device buffers of the stack's activation type.  use_graph = 1 captures
+ * the pass once per (x_dev, y_dev, rows, steps) and replays it; it needs a real stream. */
+int b200_w8a8_stack_forward(void *stack, const void *x_dev, void *y_dev, int rows, int steps, int use_graph,
+                            void *stream);
+/* Same with HOST buffers (pinned for full speed): copies in, runs, copies out, and
+ * returns after the result has landed. */
+int b200_w8a8_stack_forward_host(void *stack, const void *x_host, void *y_host, int rows, int steps, int use_graph);
+/* Switches the 16-bit activation type (fp16 <-> bf16) of later forwards; both are 2 bytes,
+ * so buffers are kept and only cached graphs are dropped. */
+int b200_w8a8_stack_set_act_dtype(void *stack, int act_dtype);
+size_t b200_w8a8_stack_device_bytes(void *stack);
+/* Kernels enqueued (or replayed) by the most recent forward. */
+long long b200_w8a8_stack_launches_per_forward(void *stack);
+
 #ifdef __cplusplus
 }
 #endif

@@ -47,6 +47,14 @@ _PROTOTYPES = {
                                  c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "b200_w8a8_packed_weight_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200_w8a8_pack_weight_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
+    "b200_w8a8_stack_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]),
+    "b200_w8a8_stack_destroy": (None, [c_void_p]),
+    "b200_w8a8_stack_set_layer": (c_int, [c_void_p, c_int] + [c_void_p] * 8 + [c_int]),
+    "b200_w8a8_stack_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_w8a8_stack_forward_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "b200_w8a8_stack_set_act_dtype": (c_int, [c_void_p, c_int]),
+    "b200_w8a8_stack_device_bytes": (c_size_t, [c_void_p]),
+    "b200_w8a8_stack_launches_per_forward": (ctypes.c_longlong, [c_void_p]),
 }
 
 _lib = None
@@ -197,3 +205,63 @@ def pack_weight(w_f32_cpu, layout=W_SLAB128, threads=0):
     _check(lib().b200_w8a8_pack_weight_host(w.data_ptr(), n, k, layout, packed.data_ptr(), scales.data_ptr(), threads),
            "pack_weight_host")
     return packed, scales
+
+
+class LinearStack:
+    """Thin holder of a b200_w8a8_stack handle (see include/b200_w8a8.h)."""
+
+    def __init__(self, d_model=2048, n_qkv=6144, d_hidden=8192, n_layers=24, max_rows=512, band_rows=0,
+                 dtype=None, eps=1e-6):
+        import torch
+        self.dtype = dtype or torch.float16
+        self.shape = (d_model, n_qkv, d_hidden, n_layers)
+        self.max_rows = max_rows
+        self.handle = lib().b200_w8a8_stack_create(d_model, n_qkv, d_hidden, n_layers, max_rows, band_rows,
+                                                   DT_F16 if self.dtype == torch.float16 else DT_BF16, eps)
+        if not self.handle:
+            raise W8A8Error("stack_create failed: " + lib().b200_w8a8_last_error().decode())
+
+    def set_layer(self, layer, weights_fp32, gammas, threads=0):
+        """weights_fp32: five CPU fp32 tensors (qkv, out, ctrl, up, down); gammas: three fp32 vectors."""
+        ws = [w.contiguous().float() for w in weights_fp32]
+        gs = [g.contiguous().float() for g in gammas]
+        _check(lib().b200_w8a8_stack_set_layer(self.handle, layer, *[w.data_ptr() for w in ws],
+                                               *[g.data_ptr() for g in gs], threads), "stack_set_layer")
+
+    def forward(self, x, y=None, steps=1, use_graph=False, stream=None):
+        import torch
+        y = torch.empty_like(x) if y is None else y
+        st = stream if stream is not None else _stream()
+        _check(lib().b200_w8a8_stack_forward(self.handle, x.data_ptr(), y.data_ptr(), x.shape[0], steps,
+                                             int(use_graph), st), "stack_forward")
+        return y
+
+    def forward_host(self, x_host, y_host, steps=1, use_graph=False):
+        _check(lib().b200_w8a8_stack_forward_host(self.handle, x_host.data_ptr(), y_host.data_ptr(), x_host.shape[0],
+                                                  steps, int(use_graph)), "stack_forward_host")
+        return y_host
+
+    def set_dtype(self, dtype):
+        import torch
+        _check(lib().b200_w8a8_stack_set_act_dtype(self.handle, DT_F16 if dtype == torch.float16 else DT_BF16),
+               "stack_set_act_dtype")
+        self.dtype = dtype
+
+    @property
+    def device_bytes(self):
+        return lib().b200_w8a8_stack_device_bytes(self.handle)
+
+    @property
+    def launches_per_forward(self):
+        return lib().b200_w8a8_stack_launches_per_forward(self.handle)
+
+    def close(self):
+        if self.handle:
+            lib().b200_w8a8_stack_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

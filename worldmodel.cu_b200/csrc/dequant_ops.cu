@@ -214,9 +214,9 @@ __global__ void __launch_bounds__(256) qkv_rms_rope_dequant_kernel(
 int dequant_residual(const int32_t *acc, const float *row_scales, const float *col_scales, const void *residual,
                      int res_dtype, const float *gate, void *out, int out_dtype, int rows, int cols,
                      cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return 0;
     if (!acc || !row_scales || !col_scales || !out || rows < 0 || cols < 0)
         return fail("invalid dequant_residual arguments rows=%d cols=%d", rows, cols);
-    if (rows == 0 || cols == 0) return 0;
     if (rows > 65535 * 1) {
         // grid.y limit: split into slabs of rows
         const int step = 65535;

@@ -1,0 +1,307 @@
+// Host-side driver of the W8A8 linear stack: owns the packed int8 weights of every layer
+// and the activation scratch, and enqueues one denoising pass (layers x the ten operators
+// of a layer) on a stream, optionally replayed as a CUDA graph.
+//
+// It is the part of the reference's runtime that sits directly above the operators,
+// restricted to the linears: weight quantization + upload
+// (wm_cuda_copy_world_layers_to_device, src/world_cuda.cu:442-539), shared scratch
+// (src/world_cuda.cu:1311-1317, 1389-1392) and the per-layer call sequence
+// (world_cuda_runtime_step_rgb, src/world_cuda.cu:1819-2330) with attention left out.
+// Differences by design: the int32 scratch is gone (epilogues read tensor memory), the
+// controller linear is a residual branch, activations are 16-bit, and rows can be walked
+// in bands so a band's intermediates stay in L2 between producer and consumer kernels.
+#include <stdio.h>
+
+#include <map>
+#include <tuple>
+#include <vector>
+
+#include "w8a8_internal.h"
+
+namespace b200 {
+
+namespace {
+
+struct Weight {
+    int8_t *codes = nullptr;
+    float *scales = nullptr;
+    int n = 0, k = 0;
+};
+
+struct Layer {
+    Weight qkv, out, ctrl, up, down;
+    float *g_attn = nullptr, *g_ctrl = nullptr, *g_mlp = nullptr;
+    bool loaded = false;
+};
+
+}  // namespace
+
+struct Stack {
+    int d = 0, n_qkv = 0, hidden = 0, n_layers = 0, max_rows = 0, band_rows = 0, dtype = B200_DT_F16;
+    float eps = 1e-6f;
+    int device = 0;
+    std::vector<Layer> layers;
+    // full-height token buffers (residual stream) and band-height scratch
+    void *tok[3] = {nullptr, nullptr, nullptr};
+    int8_t *a8 = nullptr;       // [band, max(d, hidden)]
+    float *a8_scales = nullptr; // [band]
+    void *qkv = nullptr;        // [band, n_qkv] 16-bit
+    float *h = nullptr;         // [band, hidden] fp32 hidden before re-quantization
+    void *host_stage = nullptr; // device staging for the host entry point
+    void *host_out = nullptr;
+    cudaStream_t own_stream = nullptr;
+    size_t device_bytes = 0;
+    std::map<std::tuple<const void *, void *, int, int>, cudaGraphExec_t> graphs;
+    long long launches_per_forward = 0;
+};
+
+namespace {
+
+size_t esize(int dtype) { return dtype == B200_DT_F32 ? 4 : 2; }
+
+int dev_alloc(Stack *s, void **p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes);
+    if (e != cudaSuccess) return fail("cudaMalloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
+    s->device_bytes += bytes;
+    return 0;
+}
+
+int upload_weight(Stack *s, Weight *w, const float *host, int n, int k, int threads) {
+    std::vector<int8_t> packed(packed_weight_bytes(n, k, B200_W_SLAB128));
+    std::vector<float> scales((size_t)n);
+    if (pack_weight_host(host, n, k, B200_W_SLAB128, packed.data(), scales.data(), threads)) return 1;
+    if (!w->codes) {
+        if (dev_alloc(s, (void **)&w->codes, packed.size())) return 1;
+        if (dev_alloc(s, (void **)&w->scales, (size_t)n * sizeof(float))) return 1;
+    }
+    w->n = n;
+    w->k = k;
+    cudaError_t e = cudaMemcpy(w->codes, packed.data(), packed.size(), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(w->scales, scales.data(), (size_t)n * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail("CUDA error while copying W8 weights [%d,%d]: %s", n, k, cudaGetErrorString(e));
+    return 0;
+}
+
+int upload_vec(Stack *s, float **dst, const float *host, int n) {
+    if (!*dst && dev_alloc(s, (void **)dst, (size_t)n * sizeof(float))) return 1;
+    cudaError_t e = cudaMemcpy(*dst, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail("CUDA error while copying a norm vector: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int fused(const Stack *s, const Weight &w, const int8_t *a8, const float *a8_scales, const void *residual, int act,
+          void *out, int out_dtype, long long ldo, int rows, cudaStream_t stream) {
+    LinearArgs a{};
+    a.x = a8; a.w = w.codes; a.w_layout = B200_W_SLAB128; a.m = rows; a.k = w.k; a.n = w.n;
+    a.row_scales = a8_scales; a.col_scales = w.scales; a.residual = residual; a.ldr = w.n; a.act = act;
+    a.out = out; a.ldo = ldo; a.out_dtype = out_dtype;
+    return gemm_launch(a, nullptr, 0, stream);
+}
+
+// The ten operators of one layer on rows [r0, r0+rows) of the residual stream.
+int layer_band(Stack *s, const Layer &L, const void *x, void *x1, void *x2, void *x3, int rows, cudaStream_t st) {
+    const int d = s->d, dt = s->dtype;
+    if (rms_norm_quantize_rows(x, dt, d, L.g_attn, 0, nullptr, s->a8, d, s->a8_scales, rows, d, s->eps, st)) return 1;
+    if (fused(s, L.qkv, s->a8, s->a8_scales, nullptr, B200_ACT_NONE, s->qkv, dt, s->n_qkv, rows, st)) return 1;
+    if (quantize_rows(s->qkv, dt, s->n_qkv, s->a8, d, s->a8_scales, rows, d, st)) return 1;
+    if (fused(s, L.out, s->a8, s->a8_scales, x, B200_ACT_NONE, x1, dt, d, rows, st)) return 1;
+    if (rms_norm_quantize_rows(x1, dt, d, L.g_ctrl, 0, nullptr, s->a8, d, s->a8_scales, rows, d, s->eps, st)) return 1;
+    if (fused(s, L.ctrl, s->a8, s->a8_scales, x1, B200_ACT_NONE, x2, dt, d, rows, st)) return 1;
+    if (rms_norm_quantize_rows(x2, dt, d, L.g_mlp, 0, nullptr, s->a8, d, s->a8_scales, rows, d, s->eps, st)) return 1;
+    if (fused(s, L.up, s->a8, s->a8_scales, nullptr, B200_ACT_GELU_TANH, s->h, B200_DT_F32, s->hidden, rows, st))
+        return 1;
+    if (quantize_rows(s->h, B200_DT_F32, s->hidden, s->a8, s->hidden, s->a8_scales, rows, s->hidden, st)) return 1;
+    if (fused(s, L.down, s->a8, s->a8_scales, x2, B200_ACT_NONE, x3, dt, d, rows, st)) return 1;
+    return 0;
+}
+
+int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t st) {
+    const size_t row_bytes = (size_t)s->d * esize(s->dtype);
+    const int total_layers = steps * s->n_layers;
+    long long launches = 0;
+    for (int r0 = 0; r0 < rows; r0 += s->band_rows) {
+        const int nr = rows - r0 < s->band_rows ? rows - r0 : s->band_rows;
+        const size_t off = (size_t)r0 * row_bytes;
+        const void *cur = (const char *)x + off;
+        int cur_slot = -1;  // -1: caller's input
+        for (int li = 0; li < total_layers; ++li) {
+            const Layer &L = s->layers[li % s->n_layers];
+            // Three internal buffers rotate.  x is dead once x1 exists (it is read by the
+            // first norm and as the residual of the out projection only), so the layer's
+            // result x3 may take x's buffer; the caller's input buffer is never written.
+            int free_slots[3], nf = 0;
+            for (int i = 0; i < 3; ++i)
+                if (i != cur_slot) free_slots[nf++] = i;
+            void *x1 = (char *)s->tok[free_slots[0]] + off;
+            void *x2 = (char *)s->tok[free_slots[1]] + off;
+            const int x3_slot = cur_slot >= 0 ? cur_slot : free_slots[2];
+            const bool last = li == total_layers - 1;
+            void *x3 = last ? (char *)y + off : (char *)s->tok[x3_slot] + off;
+            if (layer_band(s, L, cur, x1, x2, x3, nr, st)) return 1;
+            launches += 10;
+            cur = x3;
+            cur_slot = x3_slot;
+        }
+    }
+    s->launches_per_forward = launches;
+    return 0;
+}
+
+}  // namespace
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+void b200_w8a8_stack_destroy(void *handle);
+
+void *b200_w8a8_stack_create(int d_model, int n_qkv, int d_hidden, int n_layers, int max_rows, int band_rows,
+                             int act_dtype, float eps) {
+    if (d_model <= 0 || n_qkv < d_model || d_hidden <= 0 || n_layers <= 0 || max_rows <= 0 ||
+        (act_dtype != B200_DT_F16 && act_dtype != B200_DT_BF16) || d_model % 128 || d_hidden % 128 || n_qkv % 8) {
+        fail("invalid stack configuration d=%d n_qkv=%d hidden=%d layers=%d rows=%d dtype=%d", d_model, n_qkv,
+             d_hidden, n_layers, max_rows, act_dtype);
+        return nullptr;
+    }
+    Stack *s = new Stack();
+    s->d = d_model; s->n_qkv = n_qkv; s->hidden = d_hidden; s->n_layers = n_layers; s->max_rows = max_rows;
+    s->band_rows = band_rows > 0 && band_rows < max_rows ? band_rows : max_rows;
+    s->dtype = act_dtype; s->eps = eps;
+    s->layers.resize((size_t)n_layers);
+    cudaGetDevice(&s->device);
+    const size_t e = esize(act_dtype);
+    const int wide = d_hidden > d_model ? d_hidden : d_model;
+    bool ok = true;
+    for (int i = 0; i < 3 && ok; ++i) ok = !dev_alloc(s, &s->tok[i], (size_t)max_rows * d_model * e);
+    ok = ok && !dev_alloc(s, (void **)&s->a8, (size_t)s->band_rows * wide);
+    ok = ok && !dev_alloc(s, (void **)&s->a8_scales, (size_t)s->band_rows * sizeof(float));
+    ok = ok && !dev_alloc(s, &s->qkv, (size_t)s->band_rows * n_qkv * e);
+    ok = ok && !dev_alloc(s, (void **)&s->h, (size_t)s->band_rows * d_hidden * sizeof(float));
+    ok = ok && !dev_alloc(s, &s->host_stage, (size_t)max_rows * d_model * e);
+    ok = ok && !dev_alloc(s, &s->host_out, (size_t)max_rows * d_model * e);
+    ok = ok && cudaStreamCreateWithFlags(&s->own_stream, cudaStreamNonBlocking) == cudaSuccess;
+    if (!ok) {
+        b200_w8a8_stack_destroy(s);
+        return nullptr;
+    }
+    return s;
+}
+
+void b200_w8a8_stack_destroy(void *handle) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s) return;
+    for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);
+    for (auto &L : s->layers) {
+        Weight *ws[5] = {&L.qkv, &L.out, &L.ctrl, &L.up, &L.down};
+        for (Weight *w : ws) {
+            cudaFree(w->codes);
+            cudaFree(w->scales);
+        }
+        cudaFree(L.g_attn);
+        cudaFree(L.g_ctrl);
+        cudaFree(L.g_mlp);
+    }
+    for (int i = 0; i < 3; ++i) cudaFree(s->tok[i]);
+    cudaFree(s->a8);
+    cudaFree(s->a8_scales);
+    cudaFree(s->qkv);
+    cudaFree(s->h);
+    cudaFree(s->host_stage);
+    cudaFree(s->host_out);
+    if (s->own_stream) cudaStreamDestroy(s->own_stream);
+    delete s;
+}
+
+int b200_w8a8_stack_set_layer(void *handle, int layer, const float *w_qkv, const float *w_out, const float *w_ctrl,
+                              const float *w_up, const float *w_down, const float *g_attn, const float *g_ctrl,
+                              const float *g_mlp, int threads) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s || layer < 0 || layer >= s->n_layers || !w_qkv || !w_out || !w_ctrl || !w_up || !w_down || !g_attn ||
+        !g_ctrl || !g_mlp)
+        return fail("invalid stack_set_layer arguments (layer %d)", layer);
+    Layer &L = s->layers[(size_t)layer];
+    if (upload_weight(s, &L.qkv, w_qkv, s->n_qkv, s->d, threads)) return 1;
+    if (upload_weight(s, &L.out, w_out, s->d, s->d, threads)) return 1;
+    if (upload_weight(s, &L.ctrl, w_ctrl, s->d, s->d, threads)) return 1;
+    if (upload_weight(s, &L.up, w_up, s->hidden, s->d, threads)) return 1;
+    if (upload_weight(s, &L.down, w_down, s->d, s->hidden, threads)) return 1;
+    if (upload_vec(s, &L.g_attn, g_attn, s->d)) return 1;
+    if (upload_vec(s, &L.g_ctrl, g_ctrl, s->d)) return 1;
+    if (upload_vec(s, &L.g_mlp, g_mlp, s->d)) return 1;
+    L.loaded = true;
+    return 0;
+}
+
+int b200_w8a8_stack_set_act_dtype(void *handle, int act_dtype) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s || (act_dtype != B200_DT_F16 && act_dtype != B200_DT_BF16)) return fail("invalid stack_set_act_dtype");
+    if (act_dtype != s->dtype) {
+        for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);  // captured launches bake the type in
+        s->graphs.clear();
+        s->dtype = act_dtype;
+    }
+    return 0;
+}
+
+size_t b200_w8a8_stack_device_bytes(void *handle) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    return s ? s->device_bytes : 0;
+}
+
+long long b200_w8a8_stack_launches_per_forward(void *handle) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    return s ? s->launches_per_forward : 0;
+}
+
+int b200_w8a8_stack_forward(void *handle, const void *x_dev, void *y_dev, int rows, int steps, int use_graph,
+                            void *stream) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s || !x_dev || !y_dev || rows <= 0 || rows > s->max_rows || steps <= 0)
+        return fail("invalid stack_forward arguments rows=%d steps=%d", rows, steps);
+    for (const Layer &L : s->layers)
+        if (!L.loaded) return fail("stack_forward called before every layer was loaded");
+    cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : s->own_stream;
+    if (!use_graph) return enqueue(s, x_dev, y_dev, rows, steps, st);
+
+    auto key = std::make_tuple(x_dev, y_dev, rows, steps);
+    auto it = s->graphs.find(key);
+    if (it == s->graphs.end()) {
+        if (st == cudaStreamLegacy || stream == B200_STREAM_PER_THREAD)
+            return fail("graph replay needs a capturable stream (not a default stream)");
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+        if (e != cudaSuccess) return fail("cudaStreamBeginCapture: %s", cudaGetErrorString(e));
+        const int rc = enqueue(s, x_dev, y_dev, rows, steps, st);
+        e = cudaStreamEndCapture(st, &graph);
+        if (rc || e != cudaSuccess || !graph) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc ? 1 : fail("cudaStreamEndCapture: %s", cudaGetErrorString(e));
+        }
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return fail("cudaGraphInstantiate: %s", cudaGetErrorString(e));
+        it = s->graphs.emplace(key, exec).first;
+    }
+    cudaError_t e = cudaGraphLaunch(it->second, st);
+    if (e != cudaSuccess) return fail("cudaGraphLaunch: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int b200_w8a8_stack_forward_host(void *handle, const void *x_host, void *y_host, int rows, int steps, int use_graph) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s || !x_host || !y_host || rows <= 0 || rows > s->max_rows || steps <= 0)
+        return fail("invalid stack_forward_host arguments rows=%d steps=%d", rows, steps);
+    const size_t bytes = (size_t)rows * s->d * esize(s->dtype);
+    cudaError_t e = cudaMemcpyAsync(s->host_stage, x_host, bytes, cudaMemcpyHostToDevice, s->own_stream);
+    if (e != cudaSuccess) return fail("H2D copy: %s", cudaGetErrorString(e));
+    if (b200_w8a8_stack_forward(s, s->host_stage, s->host_out, rows, steps, use_graph, s->own_stream)) return 1;
+    e = cudaMemcpyAsync(y_host, s->host_out, bytes, cudaMemcpyDeviceToHost, s->own_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s->own_stream);
+    if (e != cudaSuccess) return fail("D2H copy / synchronize: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+}  // extern "C"

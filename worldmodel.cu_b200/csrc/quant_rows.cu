@@ -321,6 +321,7 @@ int dispatch_in_dtype(int in_dtype, const QuantArgs &a, cudaStream_t stream) {
 
 int quantize_rows(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
                   int cols, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return 0;
     if (!x || !q || !scales || rows < 0 || cols < 0 || ldx < cols || ldq < cols)
         return fail("invalid quantize_rows arguments rows=%d cols=%d", rows, cols);
     QuantArgs a{};
@@ -331,6 +332,7 @@ int quantize_rows(const void *x, int in_dtype, long long ldx, int8_t *q, long lo
 int rms_norm_quantize_rows(const void *x, int in_dtype, long long ldx, const float *vec_scale, int scale_is_mod,
                            const float *vec_bias, int8_t *q, long long ldq, float *scales, int rows, int cols,
                            float eps, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return 0;
     if (!x || !q || !scales || rows < 0 || cols < 0 || ldx < cols || ldq < cols)
         return fail("invalid rms_norm_quantize_rows arguments rows=%d cols=%d", rows, cols);
     QuantArgs a{};
@@ -342,6 +344,7 @@ int rms_norm_quantize_rows(const void *x, int in_dtype, long long ldx, const flo
 int dequant_act_quantize_rows(const int32_t *acc, long long ldacc, const float *in_row_scales,
                               const float *col_scales, const float *bias, int act, int8_t *q, long long ldq,
                               float *out_row_scales, int rows, int cols, cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return 0;
     if (!acc || !in_row_scales || !col_scales || !q || !out_row_scales || rows < 0 || cols < 0 || ldacc < cols ||
         ldq < cols || act < 0 || act > 2)
         return fail("invalid dequant_act_quantize_rows arguments rows=%d cols=%d act=%d", rows, cols, act);
