@@ -37,7 +37,7 @@ WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),
     "cfg2": (2048, 4, "bf16", 0),
-    "cfg3": (16384, 1, "fp16", 4096),   # 8 worlds x 2048 rows per GPU = the 64-world config on 8 GPUs
+    "cfg3": (16384, 1, "fp16", 2048),   # 8 worlds x 2048 rows per GPU = the 64-world config on 8 GPUs
 }
 
 

@@ -105,6 +105,17 @@ int b200_w8a8_gemm_i8_i32_can_implement(const int8_t *x_i8, const int8_t *w_i8, 
 int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, int32_t *acc_i32, int m, int k,
                           int n, void *stream);
 
+/* Tuning aid: forces the GEMM tile width (256, 128 or 64 output columns per CTA tile) for
+ * every later launch of the process; 0 restores the built-in cost model.  No counterpart in
+ * the reference, whose tile shape is a compile-time template argument
+ * (src/world_cuda_ops.cu:529-548). */
+void b200_w8a8_set_tile_width(int bn);
+/* Tuning aid: when dev_buf is non-NULL every later GEMM launch writes 8 nanosecond
+ * timestamps per CTA (entry, pipeline start, first operands landed, last MMA issued,
+ * first accumulator ready, last epilogue done, exit, unused) into the device buffer
+ * dev_buf[grid][8] of uint64.  NULL switches it off.  No counterpart in the reference. */
+void b200_w8a8_set_trace_buffer(void *dev_buf);
+
 /* One fused linear: y = store( residual + gate * act( acc * x_scales[r] * w_scales[c] + bias[c] ) )
  * with bias / gate / residual nullable, y and residual of type y_dtype (fp16, bf16 or fp32)
  * with row strides ldy / ldr.  It replaces the reference's three-call sequence

@@ -61,7 +61,9 @@ def test_each_operator_of_a_layer_against_the_oracle_on_the_same_inputs(pkg, ref
     q, s = ref.rms_norm_quantize_rows(c["x2"], lw.g_mlp, None, 1e-6, scale_is_mod=False)
     assert same(c["q4"], q) and same(c["s4"], s)
     _, _, h_ref = ref.linear_w8a8_requant(c["q4"], c["s4"], *lw.up, act=ref.ACT_GELU_TANH)
-    assert torch.allclose(c["h"], h_ref, rtol=2e-6, atol=1e-7)  # tanh differs in the last ulps
+    # the kernel evaluates GELU(tanh) as v*sigmoid(2u) on the special-function unit: a few ulp from
+    # the oracle's 0.5*v*(1+tanh(u)), whose own cancellation error for negative v is ~4e-7 absolute
+    assert torch.allclose(c["h"], h_ref, rtol=4e-6, atol=1e-6)
     q, s = ref.quantize_rows(c["h"])  # the oracle's quantizer on the GPU's own fp32 hidden
     assert same(c["q5"], q) and same(c["s5"], s)
     assert same(c["x3"], ref.linear_w8a8(c["q5"], c["s5"], *lw.down, residual=c["x2"], out_dtype=dtype))

@@ -96,6 +96,9 @@ int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, 
     return gemm_launch(raw_gemm_args(x_i8, w_i8, w_layout, acc_i32, m, k, n), nullptr, 0, as_stream(stream));
 }
 
+void b200_w8a8_set_tile_width(int bn) { gemm_set_tile_width(bn); }
+void b200_w8a8_set_trace_buffer(void *dev_buf) { gemm_set_trace_buffer(reinterpret_cast<unsigned long long *>(dev_buf)); }
+
 size_t b200_w8a8_linear_workspace_size(int m, int k, int n) { return gemm_workspace_size(m, k, n); }
 
 int b200_w8a8_linear(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,

@@ -7,16 +7,17 @@
 // separate dequant kernels that re-read its int32 scratch
 // (src/world_cuda_ops.cu:529-599, 229-262).
 //
-// Structure: a persistent kernel, one CTA per SM, 192 threads in three roles.
+// Structure: a persistent kernel, one CTA per SM, 320 threads in three roles.
 //   warp 0    : TMA producer.  Streams 128-row x 128-byte operand slabs of A and W into a
 //               ring of shared-memory stages (128-byte swizzle), signalling `full` mbarriers.
 //   warp 1    : MMA issuer.  One thread issues tcgen05.mma (kind i8, 128 x BN x 32 per
 //               instruction, four per stage) into one of two TMEM accumulators and commits
 //               completion to the stage's `empty` barrier / the accumulator's `full` barrier.
-//   warps 2-5 : epilogue.  Each owns one 32-lane TMEM sub-partition (= 32 rows of the tile),
-//               pulls accumulators out with tcgen05.ld, applies the fused epilogue in
-//               registers and stores.  The second accumulator lets tile i+1's main loop
-//               run under tile i's epilogue.
+//   warps 2-9 : epilogue.  Two warps per 32-lane TMEM sub-partition (= 32 rows of the tile),
+//               each taking half of the tile's columns: they pull accumulators out with
+//               tcgen05.ld (double-buffered in registers), apply the fused epilogue and
+//               store.  The second accumulator lets tile i+1's main loop run under tile
+//               i's epilogue.
 // Both operands are K-major in memory already, so nothing is transposed; the operand
 // descriptors only differ in height.  Every wait is bounded (see mbar_wait_bounded): on
 // expiry the CTA drains and the kernel leaves a status word instead of hanging.
@@ -24,6 +25,7 @@
 // Roofline: tensor-bound for M >= ~1024 (2*M*N*K ops), HBM-bound on the N*K weight bytes
 // for M <= 128.
 #include <cuda.h>
+#include <string.h>
 
 #include <mutex>
 #include <unordered_map>
@@ -39,8 +41,11 @@ namespace {
 
 constexpr int BM = 128;       // rows per tile = TMEM lanes
 constexpr int BK = 128;       // bytes of K per pipeline stage = one swizzle atom
-constexpr int kThreads = 192;
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kSmemBudget = 192 * 1024;          // operand pipeline
+constexpr int kStagingPerWarp = 4096;            // epilogue staging block per warp
+constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
 
 template <int BN>
 struct Cfg {
@@ -50,7 +55,7 @@ struct Cfg {
     static constexpr int kStages = kSmemBudget / kStageBytes > 10 ? 10 : kSmemBudget / kStageBytes;
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
     static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
 };
 
 struct GemmParams {
@@ -68,8 +73,14 @@ struct GemmParams {
     long long ldo;
     int out_dtype;
     int act;
-    int vec_ok;  // 16-byte vector stores/loads are legal for out / residual
+    int vec_ok;     // 16-byte vector loads of the per-column vectors / residual are legal
+    int tma_store;  // the output can be written through the TMA store path
+    unsigned long long *trace;  // tuning aid: per-CTA timestamps (8 per CTA), or null
 };
+
+__device__ __forceinline__ void trace_mark(const GemmParams &p, int slot) {
+    if (p.trace) p.trace[(size_t)blockIdx.x * 8 + slot] = global_timer_ns();
+}
 
 __device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &m_blk, int &n_blk) {
     const int per_group = p.group_m * p.num_n_blocks;
@@ -81,149 +92,245 @@ __device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &
     m_blk = gm0 + (r - n_blk * gsize);
 }
 
-// Stores 32 consecutive columns of one row.  v holds raw accumulators (as bit patterns).
-template <int BN>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t (&r)[32], int row, int col0,
-                                               float row_scale) {
-    const bool full = (col0 + 32 <= p.N) && p.vec_ok;
-    if (p.out_dtype == B200_DT_S32) {
-        int32_t *dst = reinterpret_cast<int32_t *>(p.out) + (long long)row * p.ldo + col0;
-        if (full) {
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-                reinterpret_cast<int4 *>(dst)[g] = make_int4((int)r[4 * g], (int)r[4 * g + 1], (int)r[4 * g + 2],
-                                                             (int)r[4 * g + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = (int)r[j];
-        }
-        return;
+template <int OUT>
+struct OutElem;
+template <>
+struct OutElem<B200_DT_F16> {
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
     }
+    static __device__ __forceinline__ float2 unpack(uint32_t w) {
+        return __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    }
+    static __device__ __forceinline__ float load1(const void *p, long long i) {
+        return __half2float(reinterpret_cast<const __half *>(p)[i]);
+    }
+    static __device__ __forceinline__ void store1(void *p, long long i, float v) {
+        reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
+    }
+};
+template <>
+struct OutElem<B200_DT_BF16> {
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+    static __device__ __forceinline__ float2 unpack(uint32_t w) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w));
+    }
+    static __device__ __forceinline__ float load1(const void *p, long long i) {
+        return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
+    }
+    static __device__ __forceinline__ void store1(void *p, long long i, float v) {
+        reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
+    }
+};
+template <int OUT>
+struct Out16 {
+    static constexpr int value = (OUT == B200_DT_BF16) ? B200_DT_BF16 : B200_DT_F16;
+};
 
-    float v[32];
-    if (full) {
+// fp32 epilogue values of 32 consecutive columns of one row from the accumulators in r[]
+// (registers, static indexing only).  Vector form: the chunk lies inside N and 16-byte
+// accesses to the per-column vectors and the residual are legal.
+template <int OUT>
+__device__ __forceinline__ void compute32_vec(const GemmParams &p, const uint32_t (&r)[32], int row, bool row_live,
+                                              int col0, float row_scale, const uint4 (&res16)[4], float (&v)[32]) {
+    {
+        const float4 *cs4 = reinterpret_cast<const float4 *>(p.col_scales + col0);
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-            float4 cs = __ldg(reinterpret_cast<const float4 *>(p.col_scales + col0) + g);
+            const float4 cs = __ldg(cs4 + g);
             v[4 * g + 0] = dequant_acc((int)r[4 * g + 0], row_scale, cs.x);
             v[4 * g + 1] = dequant_acc((int)r[4 * g + 1], row_scale, cs.y);
             v[4 * g + 2] = dequant_acc((int)r[4 * g + 2], row_scale, cs.z);
             v[4 * g + 3] = dequant_acc((int)r[4 * g + 3], row_scale, cs.w);
         }
-        if (p.bias) {
+    }
+    if (p.bias) {
+        const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + col0);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float4 b = __ldg(b4 + g);
+            v[4 * g + 0] = __fadd_rn(v[4 * g + 0], b.x);
+            v[4 * g + 1] = __fadd_rn(v[4 * g + 1], b.y);
+            v[4 * g + 2] = __fadd_rn(v[4 * g + 2], b.z);
+            v[4 * g + 3] = __fadd_rn(v[4 * g + 3], b.w);
+        }
+    }
+    if (p.act == B200_ACT_GELU_TANH) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = act_gelu_tanh(v[j]);
+    } else if (p.act == B200_ACT_SILU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = act_silu(v[j]);
+    }
+    if (p.gate) {
+        const float4 *g4 = reinterpret_cast<const float4 *>(p.gate + col0);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float4 b = __ldg(g4 + g);
+            v[4 * g + 0] = __fmul_rn(v[4 * g + 0], b.x);
+            v[4 * g + 1] = __fmul_rn(v[4 * g + 1], b.y);
+            v[4 * g + 2] = __fmul_rn(v[4 * g + 2], b.z);
+            v[4 * g + 3] = __fmul_rn(v[4 * g + 3], b.w);
+        }
+    }
+    if (p.residual && row_live) {
+        if (OUT == B200_DT_F32) {
+            const float4 *res = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) +
+                                                                 (long long)row * p.ldr + col0);
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
-                float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col0) + g);
-                v[4 * g + 0] = __fadd_rn(v[4 * g + 0], b.x);
-                v[4 * g + 1] = __fadd_rn(v[4 * g + 1], b.y);
-                v[4 * g + 2] = __fadd_rn(v[4 * g + 2], b.z);
-                v[4 * g + 3] = __fadd_rn(v[4 * g + 3], b.w);
+                const float4 a = res[g];
+                v[4 * g + 0] = __fadd_rn(a.x, v[4 * g + 0]);
+                v[4 * g + 1] = __fadd_rn(a.y, v[4 * g + 1]);
+                v[4 * g + 2] = __fadd_rn(a.z, v[4 * g + 2]);
+                v[4 * g + 3] = __fadd_rn(a.w, v[4 * g + 3]);
             }
-        }
-        if (p.act != B200_ACT_NONE) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = apply_act_rt(v[j], p.act);
-        }
-        if (p.gate) {
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                float4 b = __ldg(reinterpret_cast<const float4 *>(p.gate + col0) + g);
-                v[4 * g + 0] = __fmul_rn(v[4 * g + 0], b.x);
-                v[4 * g + 1] = __fmul_rn(v[4 * g + 1], b.y);
-                v[4 * g + 2] = __fmul_rn(v[4 * g + 2], b.z);
-                v[4 * g + 3] = __fmul_rn(v[4 * g + 3], b.w);
-            }
-        }
-        if (p.out_dtype == B200_DT_F32) {
-            float *dst = reinterpret_cast<float *>(p.out) + (long long)row * p.ldo + col0;
-            if (p.residual) {
-                const float4 *res =
-                    reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) +
-                                                     (long long)row * p.ldr + col0);
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    float4 a = res[g];
-                    v[4 * g + 0] = __fadd_rn(a.x, v[4 * g + 0]);
-                    v[4 * g + 1] = __fadd_rn(a.y, v[4 * g + 1]);
-                    v[4 * g + 2] = __fadd_rn(a.z, v[4 * g + 2]);
-                    v[4 * g + 3] = __fadd_rn(a.w, v[4 * g + 3]);
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-                reinterpret_cast<float4 *>(dst)[g] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         } else {
-            // 16-bit outputs: 32 columns = 64 bytes = four 16-byte vectors
-            uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + (long long)row * p.ldo + col0;
-            const bool is_half = p.out_dtype == B200_DT_F16;
-            if (p.residual) {
-                const uint4 *res = reinterpret_cast<const uint4 *>(
-                    reinterpret_cast<const uint16_t *>(p.residual) + (long long)row * p.ldr + col0);
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 raw = res[g];
-                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float2 f = is_half ? __half22float2(*reinterpret_cast<const __half2 *>(&w[i]))
-                                           : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i]));
-                        v[8 * g + 2 * i] = __fadd_rn(f.x, v[8 * g + 2 * i]);
-                        v[8 * g + 2 * i + 1] = __fadd_rn(f.y, v[8 * g + 2 * i + 1]);
-                    }
-                }
-            }
+            constexpr int O = Out16<OUT>::value;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-                uint32_t w[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    if (is_half) {
-                        __half2 h = __floats2half2_rn(v[8 * g + 2 * i], v[8 * g + 2 * i + 1]);
-                        w[i] = *reinterpret_cast<uint32_t *>(&h);
-                    } else {
-                        __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * g + 2 * i], v[8 * g + 2 * i + 1]);
-                        w[i] = *reinterpret_cast<uint32_t *>(&h);
-                    }
-                }
-                reinterpret_cast<uint4 *>(dst)[g] = make_uint4(w[0], w[1], w[2], w[3]);
+                const uint4 raw = res16[g];  // fetched one chunk ahead by the caller
+                float2 f;
+                f = OutElem<O>::unpack(raw.x); v[8 * g + 0] = __fadd_rn(f.x, v[8 * g + 0]); v[8 * g + 1] = __fadd_rn(f.y, v[8 * g + 1]);
+                f = OutElem<O>::unpack(raw.y); v[8 * g + 2] = __fadd_rn(f.x, v[8 * g + 2]); v[8 * g + 3] = __fadd_rn(f.y, v[8 * g + 3]);
+                f = OutElem<O>::unpack(raw.z); v[8 * g + 4] = __fadd_rn(f.x, v[8 * g + 4]); v[8 * g + 5] = __fadd_rn(f.y, v[8 * g + 5]);
+                f = OutElem<O>::unpack(raw.w); v[8 * g + 6] = __fadd_rn(f.x, v[8 * g + 6]); v[8 * g + 7] = __fadd_rn(f.y, v[8 * g + 7]);
             }
-        }
-        return;
-    }
-
-    // ragged edge or unaligned buffers: one element at a time
-#pragma unroll 1
-    for (int j = 0; j < 32; ++j) {
-        const int col = col0 + j;
-        if (col >= p.N) break;
-        float t = dequant_acc((int)r[j], row_scale, p.col_scales[col]);
-        if (p.bias) t = __fadd_rn(t, p.bias[col]);
-        t = apply_act_rt(t, p.act);
-        if (p.gate) t = __fmul_rn(t, p.gate[col]);
-        const long long oi = (long long)row * p.ldo + col, ri = (long long)row * p.ldr + col;
-        if (p.out_dtype == B200_DT_F32) {
-            if (p.residual) t = __fadd_rn(reinterpret_cast<const float *>(p.residual)[ri], t);
-            reinterpret_cast<float *>(p.out)[oi] = t;
-        } else if (p.out_dtype == B200_DT_F16) {
-            if (p.residual) t = __fadd_rn(__half2float(reinterpret_cast<const __half *>(p.residual)[ri]), t);
-            reinterpret_cast<__half *>(p.out)[oi] = __float2half_rn(t);
-        } else {
-            if (p.residual)
-                t = __fadd_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.residual)[ri]), t);
-            reinterpret_cast<__nv_bfloat16 *>(p.out)[oi] = __float2bfloat16_rn(t);
         }
     }
 }
 
-template <int BN>
+// Same arithmetic with every per-column access guarded: ragged right edge or unaligned vectors.
+template <int OUT>
+__device__ __forceinline__ void compute32_guarded(const GemmParams &p, const uint32_t (&r)[32], int row,
+                                                  bool row_live, int col0, float row_scale, float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const int col = col0 + j;
+        float t = 0.0f;
+        if (col < p.N) {
+            t = dequant_acc((int)r[j], row_scale, p.col_scales[col]);
+            if (p.bias) t = __fadd_rn(t, p.bias[col]);
+            t = apply_act_rt(t, p.act);
+            if (p.gate) t = __fmul_rn(t, p.gate[col]);
+            if (p.residual && row_live) {
+                const long long ri = (long long)row * p.ldr + col;
+                if (OUT == B200_DT_F32) t = __fadd_rn(reinterpret_cast<const float *>(p.residual)[ri], t);
+                else t = __fadd_rn(OutElem<Out16<OUT>::value>::load1(p.residual, ri), t);
+            }
+        }
+        v[j] = t;
+    }
+}
+
+// Direct stores of one row's 32 values (used when the output cannot be described to TMA).
+template <int OUT>
+__device__ __forceinline__ void store32_direct(const GemmParams &p, const uint32_t (&w)[32], int row, int col0) {
+    // w holds 32-bit words: raw accumulators / fp32 bit patterns, or for 16-bit types the 32 values one per word
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const int col = col0 + j;
+        if (col < p.N) {
+            const long long oi = (long long)row * p.ldo + col;
+            if (OUT == B200_DT_S32 || OUT == B200_DT_F32) reinterpret_cast<uint32_t *>(p.out)[oi] = w[j];
+            else OutElem<Out16<OUT>::value>::store1(p.out, oi, __uint_as_float(w[j]));
+        }
+    }
+}
+
+// One 32-row x 32-column block of the output per call and per warp: every thread writes its
+// row into a swizzled shared-memory staging block, lane 0 hands the block to the TMA store
+// engine, which writes whole row segments and clips at the M / N edges.  A strided per-thread
+// store of the same data costs 32 cache-line transactions per instruction instead.
+template <int OUT>
+__device__ __forceinline__ void stage_and_store(const GemmParams &p, const CUtensorMap *tm_out, uint8_t *stage,
+                                                const uint32_t (&w)[32], int lane, int row0, int col0, int seq) {
+    constexpr bool k32 = (OUT == B200_DT_S32 || OUT == B200_DT_F32);
+    // 32-bit: one 4 KB block, must be drained before reuse.  16-bit: two 2 KB blocks, alternate.
+    uint8_t *buf = k32 ? stage : stage + (seq & 1) * 2048;
+    if (lane == 0) {
+        if (k32) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    }
+    __syncwarp();
+    if (k32) {
+        uint8_t *rowp = buf + lane * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4 *>(rowp + ((c ^ (lane & 7)) << 4)) =
+                make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+    } else {
+        constexpr int O = Out16<OUT>::value;
+        uint8_t *rowp = buf + lane * 64;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4 *>(rowp + ((c ^ ((lane >> 1) & 3)) << 4)) = make_uint4(
+                OutElem<O>::pack(__uint_as_float(w[8 * c + 0]), __uint_as_float(w[8 * c + 1])),
+                OutElem<O>::pack(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3])),
+                OutElem<O>::pack(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5])),
+                OutElem<O>::pack(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7])));
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tm_out),
+                     "r"(col0), "r"(row0), "r"(smem_u32(buf))
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+}
+
+// Fetches the 16-bit residual of (row, col0 .. col0+31) into registers; issued one chunk
+// ahead of its use so that the L2 round trip hides behind the previous chunk's arithmetic.
+template <int OUT>
+__device__ __forceinline__ void fetch_residual16(const GemmParams &p, int row, int col0, uint4 (&res16)[4]) {
+    if (OUT == B200_DT_S32 || OUT == B200_DT_F32) return;
+    if (p.residual && p.vec_ok && row < p.M && col0 + 32 <= p.N) {
+        const uint4 *res = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.residual) +
+                                                           (long long)row * p.ldr + col0);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) res16[g] = res[g];
+    }
+}
+
+// GENERAL = false is the lean kernel for the common case (N a multiple of 32, aligned
+// buffers): only the vector arithmetic and the TMA store are compiled in, which keeps the
+// unrolled epilogue small enough to stay resident in the instruction cache.
+template <int OUT, bool GENERAL>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const CUtensorMap *tm_out, uint8_t *stage,
+                                               const uint32_t (&r)[32], const uint4 (&res16)[4], int lane, int row0,
+                                               int col0, float row_scale, int seq) {
+    if (GENERAL && col0 >= p.N) return;  // warp-uniform
+    const int row = row0 + lane;
+    const bool row_live = row < p.M;
+    if (OUT == B200_DT_S32) {
+        if (!GENERAL || p.tma_store) stage_and_store<OUT>(p, tm_out, stage, r, lane, row0, col0, seq);
+        else if (row_live) store32_direct<OUT>(p, r, row, col0);
+        return;
+    }
+    float v[32];
+    if (!GENERAL || (p.vec_ok && col0 + 32 <= p.N)) compute32_vec<OUT>(p, r, row, row_live, col0, row_scale, res16, v);
+    else compute32_guarded<OUT>(p, r, row, row_live, col0, row_scale, v);
+    uint32_t w[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
+    if (!GENERAL || p.tma_store) stage_and_store<OUT>(p, tm_out, stage, w, lane, row0, col0, seq);
+    else if (row_live) store32_direct<OUT>(p, w, row, col0);
+}
+
+template <int BN, int OUT, bool GENERAL>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                   const GemmParams p) {
+                   const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + C::kStages * C::kStageBytes);
+    uint8_t *staging = smem + C::kStages * C::kStageBytes;  // 1024-byte aligned: stage sizes are multiples of 1 KB
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(staging + kStagingBytes);
     uint64_t *bar_empty = bar_full + C::kStages;
     uint64_t *bar_tfull = bar_empty + C::kStages;
     uint64_t *bar_tempty = bar_tfull + 2;
@@ -234,18 +341,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
+        trace_mark(p, 0);
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bar_tfull[b], 1);
-            mbar_init(&bar_tempty[b], 4);
+            mbar_init(&bar_tempty[b], kEpilogueWarps);
         }
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
+        if (p.tma_store) tma_prefetch_desc(&tm_out);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, C::kTmemCols);
@@ -258,6 +367,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     if (warp == 0) {
         if (lane == 0) {
+            trace_mark(p, 1);
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -276,6 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
         }
+        __syncwarp();  // the whole warp must reach the closing barrier together
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_i8(BM, BN);
@@ -293,6 +404,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     ok = mbar_wait_bounded(&bar_full[s], ph, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
+                    if (t == 0 && kb == 0) trace_mark(p, 2);
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * C::kStageBytes);
                     const uint64_t da = umma_smem_desc_k128(sa);
@@ -304,40 +416,83 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (++s == C::kStages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit(&bar_tfull[b]);
+                trace_mark(p, 3);
             }
         }
+        __syncwarp();
     } else {
-        const int sub = warp & 3;  // TMEM sub-partition this warp may read
+        // Eight epilogue warps: two per TMEM sub-partition, each taking half of the columns,
+        // so every SM sub-core has two warps to hide latencies with.
+        const int ew = warp - 2;
+        const int sub = warp & 3;          // TMEM sub-partition this warp may read
+        const int half = ew >> 2;          // which half of the tile's columns
+        constexpr int kCols = BN / 2;      // columns per warp
+        constexpr int kChunks = kCols / 32;
+        uint8_t *stage = staging + ew * kStagingPerWarp;
         int t = 0;
+        int seq = 0;  // running count of this warp's staged stores: alternates the 16-bit staging halves
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
             int m_blk, n_blk;
             decode_tile(p, tile, m_blk, n_blk);
             const int b = t & 1;
             const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+            // Before the accumulator is ready: pull this warp's slice of the per-column vectors
+            // into L1, and fetch the row scale and the first residual chunk.
+            const int row0 = m_blk * BM + sub * 32;
+            const int colbase = n_blk * BN + half * kCols;
+            float row_scale = 0.0f;
+            uint4 res_a[4], res_b[4];
+            if (OUT != B200_DT_S32) {
+                const int line_col = colbase + lane * 32;  // one 128-byte line of fp32 per lane
+                if (lane * 32 < kCols && line_col < p.N) {
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(p.col_scales + line_col));
+                    if (p.bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.bias + line_col));
+                    if (p.gate) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + line_col));
+                }
+                if (row0 + lane < p.M) row_scale = __ldg(p.row_scales + row0 + lane);
+                fetch_residual16<OUT>(p, row0 + lane, colbase, res_a);
+            }
             ok = mbar_wait_bounded(&bar_tfull[b], tph, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (warp == 2 && lane == 0) trace_mark(p, 4);
             tc_fence_after_sync();
-            const int row = m_blk * BM + sub * 32 + lane;
-            const bool row_live = row < p.M;
-            const float row_scale = (row_live && p.out_dtype != B200_DT_S32) ? p.row_scales[row] : 0.0f;
-            const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * BN);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
+            const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * BN + half * kCols);
+            // two register buffers: the TMEM load (and residual fetch) of chunk c+1 is in flight
+            // while chunk c is processed
+            uint32_t ra[32], rb[32];
+            tmem_ld_32x32(taddr, ra);
+#pragma unroll
+            for (int c = 0; c < kChunks; c += 2) {
                 tmem_ld_wait();
-                const int col0 = n_blk * BN + c * 32;
-                if (row_live && col0 < p.N) epilogue_chunk<BN>(p, r, row, col0, row_scale);
+                if (c + 1 < kChunks) {
+                    tmem_ld_32x32(taddr + (uint32_t)((c + 1) * 32), rb);
+                    fetch_residual16<OUT>(p, row0 + lane, colbase + (c + 1) * 32, res_b);
+                }
+                epilogue_chunk<OUT, GENERAL>(p, &tm_out, stage, ra, res_a, lane, row0, colbase + c * 32, row_scale, seq++);
+                if (c + 1 < kChunks) {
+                    tmem_ld_wait();
+                    if (c + 2 < kChunks) {
+                        tmem_ld_32x32(taddr + (uint32_t)((c + 2) * 32), ra);
+                        fetch_residual16<OUT>(p, row0 + lane, colbase + (c + 2) * 32, res_a);
+                    }
+                    epilogue_chunk<OUT, GENERAL>(p, &tm_out, stage, rb, res_b, lane, row0, colbase + (c + 1) * 32, row_scale,
+                                        seq++);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_tempty[b]);
+            if (warp == 2 && lane == 0) trace_mark(p, 5);
         }
+        // the staging blocks must outlive the bulk stores that read them
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __syncwarp();
     }
 
     __syncthreads();
+    if (threadIdx.x == 0) trace_mark(p, 6);
     if (*abort_flag) {
         // a wait ran out somewhere: give copies and MMAs already in flight time to land
         // before the shared and tensor memory they target is released
@@ -389,9 +544,28 @@ int make_map(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint6
     return 0;
 }
 
+// Output matrix [rows, cols] of 16- or 32-bit elements, written in 32 x 32 blocks whose
+// shared-memory image uses the swizzle that makes a row-per-thread write conflict-free.
+int make_out_map(CUtensorMap *map, const void *base, int dtype, uint64_t cols, uint64_t rows, uint64_t ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
+    const bool k32 = dtype == B200_DT_S32 || dtype == B200_DT_F32;
+    const uint64_t esz = k32 ? 4 : 2;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * esz};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, k32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    k32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled (output) failed (%d)", (int)r);
+    return 0;
+}
+
 struct DeviceInfo {
     int sms = 0;
-    bool attr_set[3] = {false, false, false};
+    bool attr_set[3][4][2] = {};
 };
 DeviceInfo &device_info(int dev) {
     static DeviceInfo info[64];
@@ -402,17 +576,17 @@ DeviceInfo &device_info(int dev) {
     return d;
 }
 
-template <int BN>
-int launch_bn(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
+template <int BN, int OUT, bool GENERAL>
+int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
     using C = Cfg<BN>;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     DeviceInfo &di = device_info(dev);
-    if (!di.attr_set[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             C::kSmemBytes);
+    if (!di.attr_set[slot][OUT][GENERAL]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, OUT, GENERAL>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute(smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
-        di.attr_set[slot] = true;
+        di.attr_set[slot][OUT][GENERAL] = true;
     }
     p.num_m_blocks = (a.m + BM - 1) / BM;
     p.num_n_blocks = (a.n + BN - 1) / BN;
@@ -433,14 +607,30 @@ int launch_bn(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream)
         p.b_kx = BK;
         p.b_kz = 0;
     }
+    CUtensorMap tm_out;
+    memset(&tm_out, 0, sizeof(tm_out));
+    if (p.tma_store && make_out_map(&tm_out, a.out, a.out_dtype, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldo))
+        return 1;
     const int grid = p.num_tiles < di.sms ? p.num_tiles : di.sms;
-    gemm_i8_kernel<BN><<<grid, kThreads, C::kSmemBytes, stream>>>(tm_a, tm_b, p);
+    gemm_i8_kernel<BN, OUT, GENERAL><<<grid, kThreads, C::kSmemBytes, stream>>>(tm_a, tm_b, tm_out, p);
     return check_launch("gemm_i8_tcgen05");
+}
+
+template <int BN, int OUT>
+int launch_bn(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
+    const bool lean = p.tma_store && p.vec_ok && (a.n % 32 == 0);
+    return lean ? launch_bn_g<BN, OUT, false>(a, p, slot, stream) : launch_bn_g<BN, OUT, true>(a, p, slot, stream);
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+int g_force_bn = 0;  // tuning override of the tile width (0 = cost model)
+unsigned long long *g_trace = nullptr;  // tuning aid: device buffer for per-CTA timestamps
+
 }  // namespace
+
+void gemm_set_tile_width(int bn) { g_force_bn = bn; }
+void gemm_set_trace_buffer(unsigned long long *dev_buf) { g_trace = dev_buf; }
 
 int gemm_can_implement(const LinearArgs &a, bool verbose) {
     auto no = [&](const char *why) {
@@ -471,9 +661,10 @@ int gemm_launch(const LinearArgs &a, void *, size_t, cudaStream_t stream) {
     p.row_scales = a.row_scales; p.col_scales = a.col_scales; p.bias = a.bias; p.gate = a.gate;
     p.residual = a.residual; p.ldr = a.ldr; p.out = a.out; p.ldo = a.ldo;
     p.out_dtype = a.out_dtype; p.act = a.out_dtype == B200_DT_S32 ? 0 : a.act;
+    p.trace = g_trace;
     const size_t esz = (a.out_dtype == B200_DT_S32 || a.out_dtype == B200_DT_F32) ? 4 : 2;
-    p.vec_ok = aligned16(a.out) && ((a.ldo * esz) % 16 == 0) &&
-               (!a.residual || (aligned16(a.residual) && ((a.ldr * esz) % 16 == 0))) &&
+    p.tma_store = aligned16(a.out) && ((a.ldo * esz) % 16 == 0);
+    p.vec_ok = (!a.residual || (aligned16(a.residual) && ((a.ldr * esz) % 16 == 0))) &&
                (a.out_dtype == B200_DT_S32 ||
                 (aligned16(a.col_scales) && (!a.bias || aligned16(a.bias)) && (!a.gate || aligned16(a.gate))));
 
@@ -498,9 +689,18 @@ int gemm_launch(const LinearArgs &a, void *, size_t, cudaStream_t stream) {
             best_bn = bn;
         }
     }
-    if (best_bn == 256) return launch_bn<256>(a, p, 0, stream);
-    if (best_bn == 128) return launch_bn<128>(a, p, 1, stream);
-    return launch_bn<64>(a, p, 2, stream);
+    if (g_force_bn == 256 || g_force_bn == 128 || g_force_bn == 64) best_bn = g_force_bn;
+#define B200_LAUNCH(BN_, SLOT_)                                                       \
+    switch (a.out_dtype) {                                                            \
+        case B200_DT_S32: return launch_bn<BN_, B200_DT_S32>(a, p, SLOT_, stream);    \
+        case B200_DT_F32: return launch_bn<BN_, B200_DT_F32>(a, p, SLOT_, stream);    \
+        case B200_DT_F16: return launch_bn<BN_, B200_DT_F16>(a, p, SLOT_, stream);    \
+        default: return launch_bn<BN_, B200_DT_BF16>(a, p, SLOT_, stream);            \
+    }
+    if (best_bn == 256) { B200_LAUNCH(256, 0) }
+    if (best_bn == 128) { B200_LAUNCH(128, 1) }
+    B200_LAUNCH(64, 2)
+#undef B200_LAUNCH
 }
 
 int gemm_poll_status(int *status_out) {

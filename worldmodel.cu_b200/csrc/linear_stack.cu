@@ -262,13 +262,13 @@ int b200_w8a8_stack_forward(void *handle, const void *x_dev, void *y_dev, int ro
         return fail("invalid stack_forward arguments rows=%d steps=%d", rows, steps);
     for (const Layer &L : s->layers)
         if (!L.loaded) return fail("stack_forward called before every layer was loaded");
-    cudaStream_t st = stream ? reinterpret_cast<cudaStream_t>(stream) : s->own_stream;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);  // NULL = the legacy default stream
     if (!use_graph) return enqueue(s, x_dev, y_dev, rows, steps, st);
 
     auto key = std::make_tuple(x_dev, y_dev, rows, steps);
     auto it = s->graphs.find(key);
     if (it == s->graphs.end()) {
-        if (st == cudaStreamLegacy || stream == B200_STREAM_PER_THREAD)
+        if (!stream || st == cudaStreamLegacy || stream == B200_STREAM_PER_THREAD)
             return fail("graph replay needs a capturable stream (not a default stream)");
         cudaGraph_t graph = nullptr;
         cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);

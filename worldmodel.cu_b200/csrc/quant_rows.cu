@@ -164,8 +164,10 @@ __device__ __forceinline__ void transform8(float (&v)[8], int col, const QuantAr
     }
 }
 
-// Fast path: cols % 8 == 0, 16-byte aligned rows, cols <= G * 8 * kMaxVec.
-template <typename T, int MODE, int G>
+// Fast path: cols % 8 == 0, 16-byte aligned rows, cols <= G * 8 * NV.  NV (vectors of 8
+// elements held per thread) is a template argument so that narrow rows do not pay the
+// register footprint of wide ones: occupancy is what hides the load latency here.
+template <typename T, int MODE, int G, int NV>
 __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
     __shared__ float red_f[kThreads / 32];
     __shared__ double red_d[kThreads / 32];
@@ -177,9 +179,9 @@ __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
     const int nvec = a.cols >> 3;
 
     const T *xrow = reinterpret_cast<const T *>(a.x) + (long long)row * a.ldx;
-    float v[kMaxVec][8];
+    float v[NV][8];
 #pragma unroll
-    for (int j = 0; j < kMaxVec; ++j) {
+    for (int j = 0; j < NV; ++j) {
         int vi = gl + j * G;
         if (live && vi < nvec) {
             Load8<T>::run(xrow + 8 * vi, v[j]);
@@ -193,7 +195,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
     if (MODE == MODE_RMS) {
         double ss = 0.0;
 #pragma unroll
-        for (int j = 0; j < kMaxVec; ++j) {
+        for (int j = 0; j < NV; ++j) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 double d = (double)v[j][i];
@@ -201,7 +203,10 @@ __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
             }
         }
         ss = group_sum<G>(ss, red_d);
-        row_factor = (float)(1.0 / sqrt(ss / (double)a.cols + (double)a.eps));
+        // the fp64 divide and square root run on one lane per warp; the fp32 result is broadcast
+        float f = 0.0f;
+        if ((threadIdx.x & 31) == 0) f = (float)(1.0 / sqrt(ss / (double)a.cols + (double)a.eps));
+        row_factor = __shfl_sync(0xffffffffu, f, 0);
     } else if (MODE == MODE_DEQ_ACT) {
         // read before any store: the output scale vector may alias this one
         row_factor = live ? a.in_row_scales[row] : 0.0f;
@@ -209,7 +214,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
 
     float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < kMaxVec; ++j) {
+    for (int j = 0; j < NV; ++j) {
         int vi = gl + j * G;
         if (live && vi < nvec) {
             transform8<MODE>(v[j], 8 * vi, a, row_factor);
@@ -223,7 +228,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
 
     int8_t *qrow = a.q + (long long)row * a.ldq;
 #pragma unroll
-    for (int j = 0; j < kMaxVec; ++j) {
+    for (int j = 0; j < NV; ++j) {
         int vi = gl + j * G;
         if (live && vi < nvec) {
             uint32_t lo = 0, hi = 0;
@@ -296,13 +301,23 @@ int launch_quant(const QuantArgs &a, cudaStream_t stream) {
         quant_rows_any_kernel<T, MODE><<<a.rows, kThreads, 0, stream>>>(a);
         return check_launch("quant_rows_any");
     }
-    // A warp per row when there are many rows and the row fits 32 lanes; else a CTA per row.
-    const bool warp_rows = a.cols <= 32 * 8 * kMaxVec && (a.rows >= 4096 || a.cols <= 512);
+    // Many rows: a warp per row (no block barriers at all).  Few rows: a whole CTA per row,
+    // so that even 512 rows put work on every SM.
+    const int nvec = a.cols / 8;
+    const bool warp_rows = nvec <= 32 * kMaxVec && (a.rows >= 2048 || nvec <= 64);
     if (warp_rows) {
         constexpr int kRows = kThreads / 32;
-        quant_rows_vec_kernel<T, MODE, 32><<<(a.rows + kRows - 1) / kRows, kThreads, 0, stream>>>(a);
+        const unsigned grid = (unsigned)((a.rows + kRows - 1) / kRows);
+        if (nvec <= 32) quant_rows_vec_kernel<T, MODE, 32, 1><<<grid, kThreads, 0, stream>>>(a);
+        else if (nvec <= 64) quant_rows_vec_kernel<T, MODE, 32, 2><<<grid, kThreads, 0, stream>>>(a);
+        else if (nvec <= 128) quant_rows_vec_kernel<T, MODE, 32, 4><<<grid, kThreads, 0, stream>>>(a);
+        else quant_rows_vec_kernel<T, MODE, 32, 8><<<grid, kThreads, 0, stream>>>(a);
     } else {
-        quant_rows_vec_kernel<T, MODE, kThreads><<<a.rows, kThreads, 0, stream>>>(a);
+        const unsigned grid = (unsigned)a.rows;
+        if (nvec <= 256) quant_rows_vec_kernel<T, MODE, kThreads, 1><<<grid, kThreads, 0, stream>>>(a);
+        else if (nvec <= 512) quant_rows_vec_kernel<T, MODE, kThreads, 2><<<grid, kThreads, 0, stream>>>(a);
+        else if (nvec <= 1024) quant_rows_vec_kernel<T, MODE, kThreads, 4><<<grid, kThreads, 0, stream>>>(a);
+        else quant_rows_vec_kernel<T, MODE, kThreads, 8><<<grid, kThreads, 0, stream>>>(a);
     }
     return check_launch("quant_rows_vec");
 }
