@@ -110,6 +110,11 @@ int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, 
  * the reference, whose tile shape is a compile-time template argument
  * (src/world_cuda_ops.cu:529-548). */
 void b200_w8a8_set_tile_width(int bn);
+/* Switches programmatic dependent launch on (default) or off for every later launch of the
+ * process.  When on, a kernel of this library may be scheduled while its predecessor in the
+ * stream is still finishing, and waits on the device before it touches dependent data; off
+ * gives classic full serialization, for A/B timing.  No counterpart in the reference. */
+void b200_w8a8_set_overlapped_launch(int on);
 /* Tuning aid: when dev_buf is non-NULL every later GEMM launch writes 8 nanosecond
  * timestamps per CTA (entry, pipeline start, first operands landed, last MMA issued,
  * first accumulator ready, last epilogue done, exit, unused) into the device buffer
@@ -128,6 +133,15 @@ int b200_w8a8_linear(const int8_t *x_i8, const float *x_scales, const int8_t *w_
                      const float *w_scales, const float *bias, const float *gate, const void *residual,
                      int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
                      void *workspace, size_t workspace_bytes, void *stream);
+
+/* Same operation for weights that no work queued on `stream` writes (the normal case: weights
+ * are uploaded once).  The kernel then requests its first weight tiles while the previous
+ * kernel of the stream is still running and only waits for it before touching x, the scales,
+ * the residual and y.  This is what hides the HBM latency of chained skinny linears. */
+int b200_w8a8_linear_const_weights(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                                   const float *w_scales, const float *bias, const float *gate,
+                                   const void *residual, int64_t ldr, void *y, int y_dtype, int64_t ldy, int m,
+                                   int k, int n, int act, void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---- weights (HOST pointers) ------------------------------------------------------ */
 

@@ -149,3 +149,36 @@ def test_fused_linear_strided_output(pkg, ref):
     want = ref.linear_w8a8(a, sx, b, sw, out_dtype=torch.float16)
     assert torch.equal(buf[:, n:2 * n].cpu(), want)
     assert int(buf[:, :n].abs().max()) == 0 and int(buf[:, 2 * n:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("m,k,n", [(16, 2048, 2048), (64, 8192, 2048), (128, 2048, 8192), (32, 2048, 2048),
+                                   (100, 1024, 520), (512, 8192, 2048)])
+@pytest.mark.parametrize("forced", [0, (64 | (4 << 16)), (128 | (2 << 16)), (256 | (8 << 16))])
+def test_split_k_linear_bit_exact(pkg, ref, m, k, n, forced):
+    """Skinny / few-tile shapes with the K range split over several CTAs: integer partial sums are
+    added in the workspace, so the result is identical to the unsplit kernel and to the oracle.
+    `forced` pins tile width and split count; 0 lets the planner choose."""
+    g = torch.Generator().manual_seed(m + k)
+    a, b = codes(m, k, 11), codes(n, k, 12)
+    sx = torch.rand(m, generator=g) * 0.05 + 0.01
+    sw = torch.rand(n, generator=g) * 2e-4 + 1e-5
+    res = torch.randn(m, n, generator=g).half()
+    want = ref.linear_w8a8(a, sx, b, sw, residual=res, out_dtype=torch.float16)
+    splits = forced >> 16 if forced else 8
+    ws = torch.zeros(4096 + splits * m * n * 4, dtype=torch.uint8, device=DEV)
+    pkg.lib().b200_w8a8_set_tile_width(forced)
+    try:
+        for _ in range(2):  # twice through the same workspace: it must come back zero-filled where it matters
+            got = pkg.linear(a.to(DEV), sx.to(DEV), b.to(DEV), sw.to(DEV), residual=res.to(DEV),
+                             out_dtype=torch.float16, workspace=ws)
+            assert pkg.poll_status() == 0
+            assert torch.equal(got.cpu(), want)
+            assert int(ws[:4096].view(torch.int32).abs().max()) == 0  # ticket counters are back at zero
+    finally:
+        pkg.lib().b200_w8a8_set_tile_width(0)
+
+
+def test_split_k_planner_reports_workspace(pkg):
+    lib = pkg.lib()
+    assert lib.b200_w8a8_linear_workspace_size(16, 65536, 64) > 0       # one tile, very long K: the planner splits
+    assert lib.b200_w8a8_linear_workspace_size(16384, 2048, 6144) == 0  # plenty of tiles: no split

@@ -44,9 +44,13 @@ _PROTOTYPES = {
     "b200_w8a8_gemm_i8_i32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_set_tile_width": (None, [c_int]),
     "b200_w8a8_set_trace_buffer": (None, [c_void_p]),
+    "b200_w8a8_set_overlapped_launch": (None, [c_int]),
     "b200_w8a8_linear_workspace_size": (c_size_t, [c_int, c_int, c_int]),
     "b200_w8a8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                  c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_w8a8_linear_const_weights": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
+                                               c_size_t, c_void_p]),
     "b200_w8a8_packed_weight_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200_w8a8_pack_weight_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "b200_w8a8_stack_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]),
@@ -178,19 +182,28 @@ def gemm_i8_i32(x_i8, w_i8, n=None, w_layout=W_ROW_MAJOR):
     return acc
 
 
+def make_workspace(m, k, n, device="cuda"):
+    """Zero-filled split-K scratch for (m, k, n), or None when the planner would not split.  The
+    library keeps it zero-filled between launches, so one buffer can serve many calls in a row."""
+    import torch
+    nbytes = lib().b200_w8a8_linear_workspace_size(m, k, n)
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+
+
 def linear(x_i8, x_scales, w_i8, w_scales, n=None, w_layout=W_ROW_MAJOR, bias=None, gate=None, residual=None,
-           act=ACT_NONE, out_dtype=None, out=None):
+           act=ACT_NONE, out_dtype=None, out=None, workspace=None, const_weights=False):
     import torch
     m, k = x_i8.shape
     n = w_scales.shape[0] if n is None else n
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype or torch.float16, device=x_i8.device)
-    ws_bytes = lib().b200_w8a8_linear_workspace_size(m, k, n)
-    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x_i8.device) if ws_bytes else None
-    _check(lib().b200_w8a8_linear(_ptr(x_i8), _ptr(x_scales), _ptr(w_i8), w_layout, _ptr(w_scales), _ptr(bias),
-                                  _ptr(gate), _ptr(residual), residual.stride(0) if residual is not None else 0,
-                                  _ptr(out), _dt(out), out.stride(0), m, k, n, act, _ptr(ws), ws_bytes, _stream()),
-           "linear")
+    ws_bytes, ws = 0, None
+    if workspace is not None:
+        ws, ws_bytes = workspace, workspace.numel() * workspace.element_size()
+    fn = lib().b200_w8a8_linear_const_weights if const_weights else lib().b200_w8a8_linear
+    _check(fn(_ptr(x_i8), _ptr(x_scales), _ptr(w_i8), w_layout, _ptr(w_scales), _ptr(bias),
+              _ptr(gate), _ptr(residual), residual.stride(0) if residual is not None else 0,
+              _ptr(out), _dt(out), out.stride(0), m, k, n, act, _ptr(ws), ws_bytes, _stream()), "linear")
     return out
 
 

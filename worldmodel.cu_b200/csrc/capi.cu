@@ -31,6 +31,10 @@ int check_launch(const char *what) {
 
 const char *last_error_message() { return t_error; }
 
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
+void set_pdl_enabled(bool on) { g_pdl = on; }
+
 static inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
 }  // namespace b200
@@ -97,21 +101,39 @@ int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, 
 }
 
 void b200_w8a8_set_tile_width(int bn) { gemm_set_tile_width(bn); }
+void b200_w8a8_set_overlapped_launch(int on) { set_pdl_enabled(on != 0); }
 void b200_w8a8_set_trace_buffer(void *dev_buf) { gemm_set_trace_buffer(reinterpret_cast<unsigned long long *>(dev_buf)); }
 
 size_t b200_w8a8_linear_workspace_size(int m, int k, int n) { return gemm_workspace_size(m, k, n); }
 
-int b200_w8a8_linear(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
-                     const float *w_scales, const float *bias, const float *gate, const void *residual,
-                     int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
-                     void *workspace, size_t workspace_bytes, void *stream) {
+static int linear_impl(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                       const float *w_scales, const float *bias, const float *gate, const void *residual,
+                       int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
+                       void *workspace, size_t workspace_bytes, void *stream, int static_weights) {
     if (y_dtype == B200_DT_S32) return fail("b200_w8a8_linear writes fp16, bf16 or fp32; use gemm_i8_i32 for int32");
     LinearArgs a{};
+    a.static_weights = static_weights;
     a.x = x_i8; a.w = w_i8; a.w_layout = w_layout; a.m = m; a.k = k; a.n = n;
     a.row_scales = x_scales; a.col_scales = w_scales; a.bias = bias; a.gate = gate;
     a.residual = residual; a.ldr = residual ? ldr : ldy; a.act = act;
     a.out = y; a.ldo = ldy; a.out_dtype = y_dtype;
     return gemm_launch(a, workspace, workspace_bytes, as_stream(stream));
+}
+
+int b200_w8a8_linear(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                     const float *w_scales, const float *bias, const float *gate, const void *residual,
+                     int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
+                     void *workspace, size_t workspace_bytes, void *stream) {
+    return linear_impl(x_i8, x_scales, w_i8, w_layout, w_scales, bias, gate, residual, ldr, y, y_dtype, ldy, m, k, n,
+                       act, workspace, workspace_bytes, stream, 0);
+}
+
+int b200_w8a8_linear_const_weights(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                                   const float *w_scales, const float *bias, const float *gate,
+                                   const void *residual, int64_t ldr, void *y, int y_dtype, int64_t ldy, int m,
+                                   int k, int n, int act, void *workspace, size_t workspace_bytes, void *stream) {
+    return linear_impl(x_i8, x_scales, w_i8, w_layout, w_scales, bias, gate, residual, ldr, y, y_dtype, ldy, m, k, n,
+                       act, workspace, workspace_bytes, stream, 1);
 }
 
 size_t b200_w8a8_packed_weight_bytes(int n, int k, int layout) { return packed_weight_bytes(n, k, layout); }

@@ -31,6 +31,15 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of the library is launched so that it may start while its predecessor in the
+// stream is still draining.  pdl_trigger lets the successor be scheduled; pdl_wait blocks the
+// calling thread until every predecessor grid has completed and its writes are visible.  A
+// thread must pass pdl_wait before it reads anything a predecessor may have written and
+// before it writes anything a predecessor may still read.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

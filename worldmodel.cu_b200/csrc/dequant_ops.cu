@@ -80,6 +80,8 @@ template <typename TR, typename TO, bool VEC>
 __global__ void __launch_bounds__(256) dequant_residual_kernel(
     const int32_t *__restrict__ acc, const float *__restrict__ row_scales, const float *__restrict__ col_scales,
     const void *__restrict__ residual, const float *__restrict__ gate, void *__restrict__ out, int rows, int cols) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.y;
     const float rs = row_scales[row];
     const long long base = (long long)row * cols;
@@ -121,10 +123,10 @@ int launch_dequant_residual(const int32_t *acc, const float *rs, const float *cs
                      aligned16(out);
     if (vec) {
         dim3 grid((cols / 4 + 255) / 256, rows);
-        dequant_residual_kernel<TR, TO, true><<<grid, 256, 0, stream>>>(acc, rs, cs, res, gate, out, rows, cols);
+        launch_kernel(dequant_residual_kernel<TR, TO, true>, grid, dim3(256), 0, stream, acc, rs, cs, res, gate, out, rows, cols);
     } else {
         dim3 grid((cols + 255) / 256, rows);
-        dequant_residual_kernel<TR, TO, false><<<grid, 256, 0, stream>>>(acc, rs, cs, res, gate, out, rows, cols);
+        launch_kernel(dequant_residual_kernel<TR, TO, false>, grid, dim3(256), 0, stream, acc, rs, cs, res, gate, out, rows, cols);
     }
     return check_launch("dequant_residual");
 }
@@ -155,6 +157,8 @@ __global__ void __launch_bounds__(256) qkv_rms_rope_dequant_kernel(
     const int64_t *__restrict__ x_pos, const int64_t *__restrict__ y_pos, const int64_t *__restrict__ t_pos,
     const float *__restrict__ xy, const float *__restrict__ inv_t, int T, int n_heads, int n_kv_heads, int d_head,
     int width, int height, float eps) {
+    pdl_trigger();
+    pdl_wait();
     const int roles = n_heads + 2 * n_kv_heads;
     const long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (unit >= (long long)T * roles) return;
@@ -254,9 +258,9 @@ int qkv_rms_rope_dequant(const int32_t *qkv_acc, const float *row_scales, const 
                     d_head);
     if (tokens == 0) return 0;
     const long long units = (long long)tokens * (n_heads + 2 * n_kv_heads);
-    qkv_rms_rope_dequant_kernel<<<(unsigned)((units + 7) / 8), 256, 0, stream>>>(
-        qkv_acc, row_scales, weight_scales, q, k, v, x_pos, y_pos, t_pos, xy, inv_t, tokens, n_heads, n_kv_heads,
-        d_head, width, height, eps);
+    launch_kernel(qkv_rms_rope_dequant_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, stream, qkv_acc,
+                  row_scales, weight_scales, q, k, v, x_pos, y_pos, t_pos, xy, inv_t, tokens, n_heads, n_kv_heads,
+                  d_head, width, height, eps);
     return check_launch("qkv_rms_rope_dequant");
 }
 

@@ -62,6 +62,10 @@ struct GemmParams {
     int M, N, K;
     int num_m_blocks, num_n_blocks, num_tiles, num_k_blocks;
     int group_m;     // m-blocks per raster group (keeps a band of A resident in L2)
+    int splits, kb_per_split, num_work;  // split-K: work item = (tile, K range); num_work = tiles * splits
+    int a_stage_bytes;                   // bytes one A load delivers (fewer than 16 KB when M < 128)
+    int32_t *ws_partials;                // [splits][M][N] raw partial accumulators (split-K only)
+    int *ws_counters;                    // [tiles] arrival tickets, zero between launches
     int b_kx, b_kz;  // W coordinate multipliers: row-major (128,0), slab layout (0,1)
     const float *row_scales;
     const float *col_scales;
@@ -75,6 +79,7 @@ struct GemmParams {
     int act;
     int vec_ok;     // 16-byte vector loads of the per-column vectors / residual are legal
     int tma_store;  // the output can be written through the TMA store path
+    int static_weights;  // W may be fetched before the predecessor kernel has completed
     unsigned long long *trace;  // tuning aid: per-CTA timestamps (8 per CTA), or null
 };
 
@@ -82,6 +87,16 @@ __device__ __forceinline__ void trace_mark(const GemmParams &p, int slot) {
     if (p.trace) p.trace[(size_t)blockIdx.x * 8 + slot] = global_timer_ns();
 }
 
+__device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &m_blk, int &n_blk);
+// Work item -> (tile, split).  The splits of one tile are adjacent so that they run together.
+__device__ __forceinline__ void decode_work(const GemmParams &p, int work, int &tile, int &m_blk, int &n_blk,
+                                            int &kb0, int &kb1) {
+    const int split = work % p.splits;
+    tile = work / p.splits;
+    decode_tile(p, tile, m_blk, n_blk);
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.num_k_blocks, kb0 + p.kb_per_split);
+}
 __device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &m_blk, int &n_blk) {
     const int per_group = p.group_m * p.num_n_blocks;
     const int g = tile / per_group;
@@ -322,7 +337,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const CUtens
     else if (row_live) store32_direct<OUT>(p, w, row, col0);
 }
 
-template <int BN, int OUT, bool GENERAL>
+template <int BN, int OUT, bool GENERAL, bool SPLITK>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
@@ -336,10 +351,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint64_t *bar_tempty = bar_tfull + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *last_flag = abort_flag + 1;  // split-K: "this CTA holds the last partial of the tile"
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    pdl_trigger();  // the next kernel of the stream may be scheduled from here on
     if (threadIdx.x == 0) {
         trace_mark(p, 0);
         for (int s = 0; s < C::kStages; ++s) {
@@ -371,17 +388,40 @@ __global__ void __launch_bounds__(kThreads, 1)
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                int m_blk, n_blk;
-                decode_tile(p, tile, m_blk, n_blk);
+            // Weights that nothing in the stream writes can be requested before the predecessor
+            // kernel has finished: the first ring of W tiles is put in flight, then the thread
+            // waits for the predecessor (whose output is our A operand) and adds the A tiles.
+            int prefetched = 0;
+            if (p.static_weights && blockIdx.x < p.num_work) {
+                int tile, m_blk, n_blk, kb0, kb1;
+                decode_work(p, blockIdx.x, tile, m_blk, n_blk, kb0, kb1);
+                prefetched = min(kb1 - kb0, C::kStages);
+                for (int i = 0; i < prefetched; ++i) {
+                    uint8_t *sa = smem + i * C::kStageBytes;
+                    mbar_arrive_expect_tx(&bar_full[i], (uint32_t)(p.a_stage_bytes + C::kBBytes));
+                    tma_load_3d(sa + C::kABytes, &tm_b, &bar_full[i], (kb0 + i) * p.b_kx, n_blk * BN,
+                                (kb0 + i) * p.b_kz);
+                }
+            }
+            pdl_wait();
+            for (int work = blockIdx.x; ok && work < p.num_work; work += gridDim.x) {
+                int tile, m_blk, n_blk, kb0, kb1;
+                decode_work(p, work, tile, m_blk, n_blk, kb0, kb1);
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_EMPTY);
-                    if (!ok) break;
+                for (int kb = kb0; kb < kb1; ++kb) {
                     uint8_t *sa = smem + s * C::kStageBytes;
-                    mbar_arrive_expect_tx(&bar_full[s], C::kStageBytes);
-                    tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
-                    tma_load_3d(sa + C::kABytes, &tm_b, &bar_full[s], kb * p.b_kx, n0, kb * p.b_kz);
+                    if (prefetched > 0) {
+                        // stage already armed and its W tile already requested
+                        --prefetched;
+                        tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
+                    } else {
+                        ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag, &g_gemm_status,
+                                               KS_TIMEOUT_SMEM_EMPTY);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(p.a_stage_bytes + C::kBBytes));
+                        tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
+                        tma_load_3d(sa + C::kABytes, &tm_b, &bar_full[s], kb * p.b_kx, n0, kb * p.b_kz);
+                    }
                     if (++s == C::kStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -394,24 +434,27 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t ph = 0;
             int t = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
+            for (int work = blockIdx.x; ok && work < p.num_work; work += gridDim.x, ++t) {
+                int tile, m_blk, n_blk, kb0, kb1;
+                decode_work(p, work, tile, m_blk, n_blk, kb0, kb1);
                 const int b = t & 1;
                 const uint32_t tph = (uint32_t)(t >> 1) & 1u;
                 ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     ok = mbar_wait_bounded(&bar_full[s], ph, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
-                    if (t == 0 && kb == 0) trace_mark(p, 2);
+                    if (t == 0 && kb == kb0) trace_mark(p, 2);
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * C::kStageBytes);
                     const uint64_t da = umma_smem_desc_k128(sa);
                     const uint64_t db = umma_smem_desc_k128(sa + C::kABytes);
 #pragma unroll
                     for (int j = 0; j < BK / 32; ++j)
-                        umma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (uint32_t)((kb | j) != 0));
+                        umma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc,
+                                (uint32_t)(((kb - kb0) | j) != 0));
                     umma_commit(&bar_empty[s]);
                     if (++s == C::kStages) { s = 0; ph ^= 1u; }
                 }
@@ -429,12 +472,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         constexpr int kCols = BN / 2;      // columns per warp
         constexpr int kChunks = kCols / 32;
         uint8_t *stage = staging + ew * kStagingPerWarp;
+        pdl_wait();  // before the first read of the scales / residual and the first write of the output
         int t = 0;
         int seq = 0;  // running count of this warp's staged stores: alternates the 16-bit staging halves
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++t) {
-            int m_blk, n_blk;
-            decode_tile(p, tile, m_blk, n_blk);
+        for (int work = blockIdx.x; ok && work < p.num_work; work += gridDim.x, ++t) {
+            int tile, m_blk, n_blk, kb0, kb1;
+            decode_work(p, work, tile, m_blk, n_blk, kb0, kb1);
             const int b = t & 1;
             const uint32_t tph = (uint32_t)(t >> 1) & 1u;
             // Before the accumulator is ready: pull this warp's slice of the per-column vectors
@@ -459,6 +503,73 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (warp == 2 && lane == 0) trace_mark(p, 4);
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * BN + half * kCols);
+            if (SPLITK) {
+                // Split-K: this CTA holds one of `splits` partial sums of the tile.  Every CTA
+                // parks its raw int32 partial in the workspace and takes a ticket; the CTA that
+                // draws the last ticket adds the partials (integer sums: exact in any order)
+                // and runs the fused epilogue.  Nobody waits for anybody.
+                const int split = work % p.splits;
+                const int row = row0 + lane;
+                int32_t *mine = p.ws_partials + ((long long)split * p.M + row) * p.N;
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
+                    tmem_ld_wait();
+                    const int col0 = colbase + c * 32;
+                    if (row < p.M) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            if (col0 + 4 * g < p.N)
+                                __stcg(reinterpret_cast<int4 *>(mine + col0) + g,
+                                       make_int4((int)r[4 * g], (int)r[4 * g + 1], (int)r[4 * g + 2], (int)r[4 * g + 3]));
+                    }
+                }
+                __threadfence();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_tempty[b]);  // this warp has drained its accumulator slice
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueWarps * 32) : "memory");
+                if (ew == 0 && lane == 0) {
+                    const int old = atomicAdd(p.ws_counters + tile, 1);
+                    const int last = old == p.splits - 1;
+                    if (last) p.ws_counters[tile] = 0;  // leave the ticket counter clean for the next launch
+                    *last_flag = last;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueWarps * 32) : "memory");
+                if (*last_flag) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        const int col0 = colbase + c * 32;
+                        if (col0 >= p.N) break;
+                        uint32_t r[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                        if (row < p.M) {
+                            for (int sp = 0; sp < p.splits; ++sp) {
+                                const int4 *src = reinterpret_cast<const int4 *>(
+                                    p.ws_partials + ((long long)sp * p.M + row) * p.N + col0);
+#pragma unroll
+                                for (int g = 0; g < 8; ++g) {
+                                    if (col0 + 4 * g < p.N) {
+                                        const int4 q = __ldcg(src + g);
+                                        r[4 * g + 0] += (uint32_t)q.x;
+                                        r[4 * g + 1] += (uint32_t)q.y;
+                                        r[4 * g + 2] += (uint32_t)q.z;
+                                        r[4 * g + 3] += (uint32_t)q.w;
+                                    }
+                                }
+                            }
+                        }
+                        uint4 res[4];
+                        fetch_residual16<OUT>(p, row, col0, res);
+                        epilogue_chunk<OUT, true>(p, &tm_out, stage, r, res, lane, row0, col0, row_scale, seq++);
+                    }
+                }
+                if (warp == 2 && lane == 0) trace_mark(p, 5);
+                continue;
+            }
             // two register buffers: the TMEM load (and residual fetch) of chunk c+1 is in flight
             // while chunk c is processed
             uint32_t ra[32], rb[32];
@@ -565,7 +676,7 @@ int make_out_map(CUtensorMap *map, const void *base, int dtype, uint64_t cols, u
 
 struct DeviceInfo {
     int sms = 0;
-    bool attr_set[3][4][2] = {};
+    bool attr_set[3][4][3] = {};
 };
 DeviceInfo &device_info(int dev) {
     static DeviceInfo info[64];
@@ -576,26 +687,35 @@ DeviceInfo &device_info(int dev) {
     return d;
 }
 
-template <int BN, int OUT, bool GENERAL>
+template <int BN, int OUT, bool GENERAL, bool SPLITK>
 int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
     using C = Cfg<BN>;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     DeviceInfo &di = device_info(dev);
-    if (!di.attr_set[slot][OUT][GENERAL]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, OUT, GENERAL>,
+    constexpr int kVariant = SPLITK ? 2 : (GENERAL ? 1 : 0);
+    if (!di.attr_set[slot][OUT][kVariant]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute(smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
-        di.attr_set[slot][OUT][GENERAL] = true;
+        di.attr_set[slot][OUT][kVariant] = true;
     }
     p.num_m_blocks = (a.m + BM - 1) / BM;
     p.num_n_blocks = (a.n + BN - 1) / BN;
     p.num_tiles = p.num_m_blocks * p.num_n_blocks;
     p.num_k_blocks = (a.k + BK - 1) / BK;
     p.group_m = 32;
+    if (p.splits < 1) p.splits = 1;
+    p.kb_per_split = (p.num_k_blocks + p.splits - 1) / p.splits;
+    p.num_work = p.num_tiles * p.splits;
+    // fewer than 128 rows: load only the rows that exist (the MMA still spans 128 lanes; the
+    // lanes beyond M multiply whatever the stage held before and are never read back)
+    const int a_rows = a.m >= BM ? BM : ((a.m + 15) / 16) * 16;
+    p.a_stage_bytes = a_rows * BK;
 
     CUtensorMap tm_a, tm_b;
-    if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m, BM))
+    if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m,
+                 (uint32_t)a_rows))
         return 1;
     if (a.w_layout == B200_W_SLAB128) {
         if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, BN)) return 1;
@@ -611,15 +731,19 @@ int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t strea
     memset(&tm_out, 0, sizeof(tm_out));
     if (p.tma_store && make_out_map(&tm_out, a.out, a.out_dtype, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldo))
         return 1;
-    const int grid = p.num_tiles < di.sms ? p.num_tiles : di.sms;
-    gemm_i8_kernel<BN, OUT, GENERAL><<<grid, kThreads, C::kSmemBytes, stream>>>(tm_a, tm_b, tm_out, p);
+    const int grid = p.num_work < di.sms ? p.num_work : di.sms;
+    cudaError_t le = launch_kernel(gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>, dim3(grid), dim3(kThreads),
+                                   (size_t)C::kSmemBytes, stream, tm_a, tm_b, tm_out, p);
+    if (le != cudaSuccess) return fail("launching gemm_i8_tcgen05: %s", cudaGetErrorString(le));
     return check_launch("gemm_i8_tcgen05");
 }
 
 template <int BN, int OUT>
 int launch_bn(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
+    if (p.splits > 1) return launch_bn_g<BN, OUT, true, true>(a, p, slot, stream);
     const bool lean = p.tma_store && p.vec_ok && (a.n % 32 == 0);
-    return lean ? launch_bn_g<BN, OUT, false>(a, p, slot, stream) : launch_bn_g<BN, OUT, true>(a, p, slot, stream);
+    return lean ? launch_bn_g<BN, OUT, false, false>(a, p, slot, stream)
+                : launch_bn_g<BN, OUT, true, false>(a, p, slot, stream);
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -652,9 +776,66 @@ int gemm_can_implement(const LinearArgs &a, bool verbose) {
     return 0;
 }
 
-size_t gemm_workspace_size(int, int, int) { return 0; }
+namespace {
 
-int gemm_launch(const LinearArgs &a, void *, size_t, cudaStream_t stream) {
+constexpr size_t kCounterBytes = 4096;  // ticket counters at the head of the workspace (1024 tiles)
+
+struct Plan {
+    int bn = 256;
+    int splits = 1;
+};
+
+// Picks the tile width and the K split from a small time model (microseconds).  A tile costs
+// its K slabs (bounded by the MMA rate and by how fast one SM can pull operands), its
+// epilogue and, when K is split, the partial-sum exchange; tiles run in waves over the SMs.
+Plan make_plan(int m, int k, int n, int sms, bool allow_split) {
+    const int mb = (m + BM - 1) / BM;
+    const int kblocks = (k + BK - 1) / BK;
+    const double a_kb = (m >= BM ? BM : ((m + 15) / 16) * 16) * (double)BK / 1024.0;
+    Plan best;
+    double best_t = 1e30;
+    const int widths[3] = {256, 128, 64};
+    for (int wi = 0; wi < 3; ++wi) {
+        const int bn = widths[wi];
+        const long long tiles = (long long)mb * ((n + bn - 1) / bn);
+        const int max_splits = (allow_split && (n % 4) == 0 && tiles < sms && tiles <= 1024) ? 8 : 1;
+        for (int sp = 1; sp <= max_splits; ++sp) {
+            if (sp > 1 && kblocks / sp < 2) break;
+            const long long work = tiles * sp;
+            if (sp > 1 && work > sms) break;  // keep all partials of a launch in one wave
+            const int kbps = (kblocks + sp - 1) / sp;
+            const double waves = (double)((work + sms - 1) / sms);
+            const double t_mma = 0.065 * bn / 64.0;
+            const double t_load = (a_kb + bn * (double)BK / 1024.0) / 150.0;  // ~150 KB/us per SM
+            const double t_epi = 0.45 * bn / 64.0;
+            const double t_red = sp > 1 ? 3.0 + 1.0 * sp * bn / 64.0 : 0.0;  // measured: fences + serial partial reads
+            const double t = waves * (0.3 + kbps * (t_mma > t_load ? t_mma : t_load) + t_epi + t_red);
+            if (t < best_t) {
+                best_t = t;
+                best.bn = bn;
+                best.splits = sp;
+            }
+        }
+    }
+    return best;
+}
+
+int device_sms() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int sms = device_info(dev).sms;
+    return sms > 0 ? sms : 148;
+}
+
+}  // namespace
+
+size_t gemm_workspace_size(int m, int k, int n) {
+    if (m <= 0 || k <= 0 || n <= 0) return 0;
+    const Plan pl = make_plan(m, k, n, device_sms(), true);
+    return pl.splits > 1 ? kCounterBytes + (size_t)pl.splits * (size_t)m * (size_t)n * sizeof(int32_t) : 0;
+}
+
+int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
     if (gemm_can_implement(a, true)) return 1;
     GemmParams p{};
     p.M = a.m; p.N = a.n; p.K = a.k;
@@ -662,34 +843,30 @@ int gemm_launch(const LinearArgs &a, void *, size_t, cudaStream_t stream) {
     p.residual = a.residual; p.ldr = a.ldr; p.out = a.out; p.ldo = a.ldo;
     p.out_dtype = a.out_dtype; p.act = a.out_dtype == B200_DT_S32 ? 0 : a.act;
     p.trace = g_trace;
+    p.static_weights = a.static_weights;
     const size_t esz = (a.out_dtype == B200_DT_S32 || a.out_dtype == B200_DT_F32) ? 4 : 2;
     p.tma_store = aligned16(a.out) && ((a.ldo * esz) % 16 == 0);
     p.vec_ok = (!a.residual || (aligned16(a.residual) && ((a.ldr * esz) % 16 == 0))) &&
                (a.out_dtype == B200_DT_S32 ||
                 (aligned16(a.col_scales) && (!a.bias || aligned16(a.bias)) && (!a.gate || aligned16(a.gate))));
 
-    // Tile width: the widest tile is the most efficient per MMA, but a grid that leaves
-    // most SMs idle loses more.  Cost model: waves x width.
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int sms = device_info(dev).sms > 0 ? device_info(dev).sms : 148;
-    const int mb = (a.m + BM - 1) / BM;
-    int best_bn = 256;
-    long long best_cost = -1;
-    const int widths[3] = {256, 128, 64};
-    for (int i = 0; i < 3; ++i) {
-        const int bn = widths[i];
-        const long long tiles = (long long)mb * ((a.n + bn - 1) / bn);
-        const long long waves = (tiles + sms - 1) / sms;
-        // relative time of one K-slab: N=64 MMAs are limited by re-reading the A operand
-        // from shared memory, so they cost more than a quarter of an N=256 MMA
-        const long long cost = waves * ((bn == 64 ? 96 : bn) + 16);  // +16: fixed per-tile overhead
-        if (best_cost < 0 || cost < best_cost) {
-            best_cost = cost;
-            best_bn = bn;
+    const bool ws_ok = workspace && aligned16(workspace);
+    Plan pl = make_plan(a.m, a.k, a.n, device_sms(), ws_ok);
+    const int force_bn = g_force_bn & 0xFFFF, force_splits = g_force_bn >> 16;
+    if (force_bn == 256 || force_bn == 128 || force_bn == 64) pl.bn = force_bn;
+    if (force_splits >= 1) pl.splits = force_splits;
+    if (pl.splits > 1) {
+        const size_t need = kCounterBytes + (size_t)pl.splits * (size_t)a.m * (size_t)a.n * sizeof(int32_t);
+        const long long tiles = (long long)((a.m + BM - 1) / BM) * ((a.n + pl.bn - 1) / pl.bn);
+        if (!ws_ok || workspace_bytes < need || tiles > 1024 || (a.n % 4) != 0) {
+            if (force_splits > 1) return fail("split-K needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+            pl = make_plan(a.m, a.k, a.n, device_sms(), false);
+        } else {
+            p.ws_counters = reinterpret_cast<int *>(workspace);
+            p.ws_partials = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(workspace) + kCounterBytes);
         }
     }
-    if (g_force_bn == 256 || g_force_bn == 128 || g_force_bn == 64) best_bn = g_force_bn;
+    p.splits = pl.splits;
 #define B200_LAUNCH(BN_, SLOT_)                                                       \
     switch (a.out_dtype) {                                                            \
         case B200_DT_S32: return launch_bn<BN_, B200_DT_S32>(a, p, SLOT_, stream);    \
@@ -697,8 +874,8 @@ int gemm_launch(const LinearArgs &a, void *, size_t, cudaStream_t stream) {
         case B200_DT_F16: return launch_bn<BN_, B200_DT_F16>(a, p, SLOT_, stream);    \
         default: return launch_bn<BN_, B200_DT_BF16>(a, p, SLOT_, stream);            \
     }
-    if (best_bn == 256) { B200_LAUNCH(256, 0) }
-    if (best_bn == 128) { B200_LAUNCH(128, 1) }
+    if (pl.bn == 256) { B200_LAUNCH(256, 0) }
+    if (pl.bn == 128) { B200_LAUNCH(128, 1) }
     B200_LAUNCH(64, 2)
 #undef B200_LAUNCH
 }

@@ -95,6 +95,7 @@ int fused(const Stack *s, const Weight &w, const int8_t *a8, const float *a8_sca
     a.x = a8; a.w = w.codes; a.w_layout = B200_W_SLAB128; a.m = rows; a.k = w.k; a.n = w.n;
     a.row_scales = a8_scales; a.col_scales = w.scales; a.residual = residual; a.ldr = w.n; a.act = act;
     a.out = out; a.ldo = ldo; a.out_dtype = out_dtype;
+    a.static_weights = 1;  // the stack's weights are written only by set_layer, which blocks
     return gemm_launch(a, nullptr, 0, stream);
 }
 

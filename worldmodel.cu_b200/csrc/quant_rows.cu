@@ -171,6 +171,8 @@ template <typename T, int MODE, int G, int NV>
 __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
     __shared__ float red_f[kThreads / 32];
     __shared__ double red_d[kThreads / 32];
+    pdl_trigger();
+    pdl_wait();
     constexpr int kRowsPerCta = kThreads / G;
     const int gid = threadIdx.x / G;
     const int gl = threadIdx.x % G;
@@ -248,6 +250,8 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads) quant_rows_any_kernel(QuantArgs a) {
     __shared__ float red_f[kThreads / 32];
     __shared__ double red_d[kThreads / 32];
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const T *xrow = reinterpret_cast<const T *>(a.x) + (long long)row * a.ldx;
 
@@ -298,7 +302,7 @@ int launch_quant(const QuantArgs &a, cudaStream_t stream) {
     if (MODE == MODE_RMS) vec_ok = vec_ok && (!a.vec_scale || aligned16(a.vec_scale)) && (!a.vec_bias || aligned16(a.vec_bias));
     if (MODE == MODE_DEQ_ACT) vec_ok = vec_ok && aligned16(a.col_scales) && (!a.vec_bias || aligned16(a.vec_bias));
     if (!vec_ok) {
-        quant_rows_any_kernel<T, MODE><<<a.rows, kThreads, 0, stream>>>(a);
+        launch_kernel(quant_rows_any_kernel<T, MODE>, dim3(a.rows), dim3(kThreads), 0, stream, a);
         return check_launch("quant_rows_any");
     }
     // Many rows: a warp per row (no block barriers at all).  Few rows: a whole CTA per row,
@@ -308,16 +312,16 @@ int launch_quant(const QuantArgs &a, cudaStream_t stream) {
     if (warp_rows) {
         constexpr int kRows = kThreads / 32;
         const unsigned grid = (unsigned)((a.rows + kRows - 1) / kRows);
-        if (nvec <= 32) quant_rows_vec_kernel<T, MODE, 32, 1><<<grid, kThreads, 0, stream>>>(a);
-        else if (nvec <= 64) quant_rows_vec_kernel<T, MODE, 32, 2><<<grid, kThreads, 0, stream>>>(a);
-        else if (nvec <= 128) quant_rows_vec_kernel<T, MODE, 32, 4><<<grid, kThreads, 0, stream>>>(a);
-        else quant_rows_vec_kernel<T, MODE, 32, 8><<<grid, kThreads, 0, stream>>>(a);
+        if (nvec <= 32) launch_kernel(quant_rows_vec_kernel<T, MODE, 32, 1>, dim3(grid), dim3(kThreads), 0, stream, a);
+        else if (nvec <= 64) launch_kernel(quant_rows_vec_kernel<T, MODE, 32, 2>, dim3(grid), dim3(kThreads), 0, stream, a);
+        else if (nvec <= 128) launch_kernel(quant_rows_vec_kernel<T, MODE, 32, 4>, dim3(grid), dim3(kThreads), 0, stream, a);
+        else launch_kernel(quant_rows_vec_kernel<T, MODE, 32, 8>, dim3(grid), dim3(kThreads), 0, stream, a);
     } else {
         const unsigned grid = (unsigned)a.rows;
-        if (nvec <= 256) quant_rows_vec_kernel<T, MODE, kThreads, 1><<<grid, kThreads, 0, stream>>>(a);
-        else if (nvec <= 512) quant_rows_vec_kernel<T, MODE, kThreads, 2><<<grid, kThreads, 0, stream>>>(a);
-        else if (nvec <= 1024) quant_rows_vec_kernel<T, MODE, kThreads, 4><<<grid, kThreads, 0, stream>>>(a);
-        else quant_rows_vec_kernel<T, MODE, kThreads, 8><<<grid, kThreads, 0, stream>>>(a);
+        if (nvec <= 256) launch_kernel(quant_rows_vec_kernel<T, MODE, kThreads, 1>, dim3(grid), dim3(kThreads), 0, stream, a);
+        else if (nvec <= 512) launch_kernel(quant_rows_vec_kernel<T, MODE, kThreads, 2>, dim3(grid), dim3(kThreads), 0, stream, a);
+        else if (nvec <= 1024) launch_kernel(quant_rows_vec_kernel<T, MODE, kThreads, 4>, dim3(grid), dim3(kThreads), 0, stream, a);
+        else launch_kernel(quant_rows_vec_kernel<T, MODE, kThreads, 8>, dim3(grid), dim3(kThreads), 0, stream, a);
     }
     return check_launch("quant_rows_vec");
 }

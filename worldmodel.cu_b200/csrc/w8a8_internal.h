@@ -18,6 +18,27 @@ int fail(const char *fmt, ...);
 int check_launch(const char *what);
 const char *last_error_message();
 
+// Launches with programmatic stream serialization: the kernel may begin while its predecessor
+// in the stream is finishing; every kernel of the library guards its global accesses with
+// griddepcontrol.wait.  pdl_enabled() can be switched off for A/B timing.
+bool pdl_enabled();
+void set_pdl_enabled(bool on);
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- quant_rows.cu
 int quantize_rows(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
                   int cols, cudaStream_t stream);
@@ -54,6 +75,8 @@ struct LinearArgs {
     void *out;                // [m, ldo]
     long long ldo;
     int out_dtype;            // B200_DT_S32 means raw accumulators, epilogue inputs ignored
+    int static_weights;       // w is never written by work queued on the stream: its first tiles may be
+                              // fetched before the predecessor kernel has finished
 };
 int gemm_can_implement(const LinearArgs &a, bool verbose);
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
