@@ -143,6 +143,28 @@ int b200_w8a8_linear_const_weights(const int8_t *x_i8, const float *x_scales, co
                                    const void *residual, int64_t ldr, void *y, int y_dtype, int64_t ldy, int m,
                                    int k, int n, int act, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The fused linear for callers that must not allocate device memory: code running under a
+ * memory budget that is fixed at start-up, inside a region where the allocator may not be
+ * entered (a real-time render / control loop, a callback from another runtime), or in a
+ * process whose device memory is fully handed out to another framework.  It is the split-K
+ * form of b200_w8a8_linear (same arguments minus the workspace, same results bit for bit);
+ * its partial sums and ticket counters live in a scratch array that is part of the library
+ * image: 8 MiB + 4 KiB, held on every GPU that loads the library until the process exits.
+ * Limits: K >= 512, N % 4 == 0, and splits * M * N * 4 + 4096 bytes must fit the scratch
+ * (b200_w8a8_linear_static_scratch_capacity()); larger shapes are rejected with a message,
+ * never truncated.  It calls no cudaMalloc / cudaFree or other allocating routine.
+ * The first call on each device looks up the scratch's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * All calls share the one scratch: two calls whose kernels can overlap on the GPU (different
+ * streams, or different host threads on one device) race on it; calls on one stream are
+ * safe, each launch leaves the counters zeroed for the next.
+ * This entry point has no counterpart in the reference. */
+size_t b200_w8a8_linear_static_scratch_capacity(void);
+int b200_w8a8_linear_static_scratch(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                                    const float *w_scales, const float *bias, const float *gate,
+                                    const void *residual, int64_t ldr, void *y, int y_dtype, int64_t ldy, int m,
+                                    int k, int n, int act, void *stream);
+
 /* ---- weights (HOST pointers) ------------------------------------------------------ */
 
 /* Per-output-channel symmetric int8 quantization of host fp32 w[N,K] into `layout`,

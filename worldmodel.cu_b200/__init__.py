@@ -51,6 +51,9 @@ _PROTOTYPES = {
     "b200_w8a8_linear_const_weights": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p,
                                                c_size_t, c_void_p]),
+    "b200_w8a8_linear_static_scratch_capacity": (c_size_t, []),
+    "b200_w8a8_linear_static_scratch": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_packed_weight_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200_w8a8_pack_weight_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "b200_w8a8_stack_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]),
@@ -204,6 +207,19 @@ def linear(x_i8, x_scales, w_i8, w_scales, n=None, w_layout=W_ROW_MAJOR, bias=No
     _check(fn(_ptr(x_i8), _ptr(x_scales), _ptr(w_i8), w_layout, _ptr(w_scales), _ptr(bias),
               _ptr(gate), _ptr(residual), residual.stride(0) if residual is not None else 0,
               _ptr(out), _dt(out), out.stride(0), m, k, n, act, _ptr(ws), ws_bytes, _stream()), "linear")
+    return out
+
+
+def linear_static_scratch(x_i8, x_scales, w_i8, w_scales, n=None, w_layout=W_ROW_MAJOR, bias=None, gate=None,
+                          residual=None, act=ACT_NONE, out=None):
+    """The no-allocation entry point: `out` must be supplied, nothing is allocated on the way."""
+    m, k = x_i8.shape
+    n = w_scales.shape[0] if n is None else n
+    _check(lib().b200_w8a8_linear_static_scratch(_ptr(x_i8), _ptr(x_scales), _ptr(w_i8), w_layout, _ptr(w_scales),
+                                                 _ptr(bias), _ptr(gate), _ptr(residual),
+                                                 residual.stride(0) if residual is not None else 0, _ptr(out),
+                                                 _dt(out), out.stride(0), m, k, n, act, _stream()),
+           "linear_static_scratch")
     return out
 
 

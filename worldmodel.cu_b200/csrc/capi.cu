@@ -136,6 +136,21 @@ int b200_w8a8_linear_const_weights(const int8_t *x_i8, const float *x_scales, co
                        act, workspace, workspace_bytes, stream, 1);
 }
 
+size_t b200_w8a8_linear_static_scratch_capacity(void) { return static_scratch_capacity(); }
+
+int b200_w8a8_linear_static_scratch(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                                    const float *w_scales, const float *bias, const float *gate,
+                                    const void *residual, int64_t ldr, void *y, int y_dtype, int64_t ldy, int m,
+                                    int k, int n, int act, void *stream) {
+    if (y_dtype == B200_DT_S32) return fail("b200_w8a8_linear_static_scratch writes fp16, bf16 or fp32");
+    LinearArgs a{};
+    a.x = x_i8; a.w = w_i8; a.w_layout = w_layout; a.m = m; a.k = k; a.n = n;
+    a.row_scales = x_scales; a.col_scales = w_scales; a.bias = bias; a.gate = gate;
+    a.residual = residual; a.ldr = residual ? ldr : ldy; a.act = act;
+    a.out = y; a.ldo = ldy; a.out_dtype = y_dtype;
+    return linear_static_scratch(a, as_stream(stream));
+}
+
 size_t b200_w8a8_packed_weight_bytes(int n, int k, int layout) { return packed_weight_bytes(n, k, layout); }
 
 int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,

@@ -37,6 +37,13 @@ namespace b200 {
 
 __device__ int g_gemm_status = 0;
 
+// Built-in split-K scratch for callers that cannot allocate device memory (see
+// linear_static_scratch below).  It lives in the module's global segment: every GPU that
+// loads the library holds these bytes until the process exits.  Zero-initialized at load;
+// the split-K kernel returns its ticket counters to zero, so it is ready again after each call.
+constexpr size_t kStaticScratchBytes = 4096 + (size_t)8 * 1024 * 1024;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 namespace {
 
 constexpr int BM = 128;       // rows per tile = TMEM lanes
@@ -835,7 +842,18 @@ size_t gemm_workspace_size(int m, int k, int n) {
     return pl.splits > 1 ? kCounterBytes + (size_t)pl.splits * (size_t)m * (size_t)n * sizeof(int32_t) : 0;
 }
 
+namespace {
+int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream,
+                     const Plan *fixed_plan);
+}
+
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    return gemm_launch_impl(a, workspace, workspace_bytes, stream, nullptr);
+}
+
+namespace {
+int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream,
+                     const Plan *fixed_plan) {
     if (gemm_can_implement(a, true)) return 1;
     GemmParams p{};
     p.M = a.m; p.N = a.n; p.K = a.k;
@@ -852,7 +870,11 @@ int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cu
 
     const bool ws_ok = workspace && aligned16(workspace);
     Plan pl = make_plan(a.m, a.k, a.n, device_sms(), ws_ok);
-    const int force_bn = g_force_bn & 0xFFFF, force_splits = g_force_bn >> 16;
+    int force_bn = g_force_bn & 0xFFFF, force_splits = g_force_bn >> 16;
+    if (fixed_plan) {
+        force_bn = fixed_plan->bn;
+        force_splits = fixed_plan->splits;
+    }
     if (force_bn == 256 || force_bn == 128 || force_bn == 64) pl.bn = force_bn;
     if (force_splits >= 1) pl.splits = force_splits;
     if (pl.splits > 1) {
@@ -878,6 +900,44 @@ int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cu
     if (pl.bn == 128) { B200_LAUNCH(128, 1) }
     B200_LAUNCH(64, 2)
 #undef B200_LAUNCH
+}
+}  // namespace
+
+size_t static_scratch_capacity() { return kStaticScratchBytes; }
+
+int linear_static_scratch(const LinearArgs &a, cudaStream_t stream) {
+    if (gemm_can_implement(a, true)) return 1;
+    // The array's name is only a host-side handle; the kernel needs the device address, which is
+    // looked up once per device, with that device current.
+    static void *scratch_addr[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail("cudaGetDevice failed");
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!scratch_addr[dev]) {
+            void *ptr = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+            if (e != cudaSuccess || !ptr) return fail("cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+            scratch_addr[dev] = ptr;
+        }
+        scratch = scratch_addr[dev];
+    }
+    // This entry point always splits K (that is what needs the scratch): the planner's split
+    // if it chose one, else two halves.
+    const int kblocks = (a.k + BK - 1) / BK;
+    if (kblocks < 4 || (a.n % 4) != 0)
+        return fail("the no-allocation linear needs K >= 512 and N %% 4 == 0, got K=%d N=%d", a.k, a.n);
+    Plan pl = make_plan(a.m, a.k, a.n, device_sms(), true);
+    if (pl.splits < 2) pl.splits = 2;
+    const long long tiles = (long long)((a.m + BM - 1) / BM) * ((a.n + pl.bn - 1) / pl.bn);
+    const size_t need = kCounterBytes + (size_t)pl.splits * (size_t)a.m * (size_t)a.n * sizeof(int32_t);
+    if (need > kStaticScratchBytes || tiles > 1024)
+        return fail("M=%d N=%d with %d K-splits needs %zu bytes of scratch; the built-in scratch holds %zu "
+                    "(use b200_w8a8_linear with a caller-allocated workspace instead)",
+                    a.m, a.n, pl.splits, need, kStaticScratchBytes);
+    return gemm_launch_impl(a, scratch, kStaticScratchBytes, stream, &pl);
 }
 
 int gemm_poll_status(int *status_out) {

@@ -82,6 +82,8 @@ int gemm_can_implement(const LinearArgs &a, bool verbose);
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemm_workspace_size(int m, int k, int n);
 int gemm_poll_status(int *status_out);
+int linear_static_scratch(const LinearArgs &a, cudaStream_t stream);
+size_t static_scratch_capacity();
 void gemm_set_tile_width(int bn);
 void gemm_set_trace_buffer(unsigned long long *dev_buf);
 
