@@ -33,6 +33,7 @@ LINEARS = [("qkv", N_QKV, D_MODEL), ("out", D_MODEL, D_MODEL), ("ctrl", D_MODEL,
            ("up", D_HIDDEN, D_MODEL), ("down", D_MODEL, D_HIDDEN)]
 OPS_PER_ROW_LAYER = 2 * sum(n * k for _, n, k in LINEARS)  # 109,051,904
 WEIGHT_BYTES_LAYER = sum(n * k for _, n, k in LINEARS)     # 54,525,952
+NCU_DRAM_BYTES_PER_LAYER_M512 = 69.5e6
 WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),
@@ -284,6 +285,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configs reported under `extras`")
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers of the stack (24 = the real workload)")
+    ap.add_argument("--only-gemms", type=int, default=0, metavar="ROWS",
+                    help="run the five fused linears of one layer at ROWS rows for --steps rounds with distinct "
+                         "weights and exit (a small, self-ending case for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -305,6 +309,8 @@ def main():
 
     pkg, ref = load_package(), load_oracle()
     pkg.lib()  # raises if the CUDA library is missing
+    if args.only_gemms:
+        return run_only_gemms(pkg, args.only_gemms, max(args.steps, 1))
     peaks = measured_peaks()
     rows, chained, dt_name, band = WORKLOADS[args.workload]
     dtype = torch.float16 if dt_name == "fp16" else torch.bfloat16
@@ -368,8 +374,13 @@ def main():
     int8_peak = 2.0 * peaks["bf16_tflops"]  # tcgen05 int8 issues at twice the bf16 rate
     achieved = gemm_ops / gemm_s / 1e12
     weight_gbs = WEIGHT_BYTES_LAYER / gemm_s / 1e9
+    # DRAM bytes of the five launches of one layer from the committed ncu capture (profiles/), M=512 only
+    traffic = NCU_DRAM_BYTES_PER_LAYER_M512 if rows == 512 else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                "frac": achieved / int8_peak, "traffic": None,
+                "frac": achieved / int8_peak, "traffic": traffic,
+                "traffic_note": "dram read+write summed over the five GEMM launches of one layer (ncu, profiles/"
+                                "gemm_i8_kernel_layer_m512.md); algorithmic bytes of the same launches: "
+                                f"{(WEIGHT_BYTES_LAYER + rows * (4 * D_MODEL + D_HIDDEN) + 3 * rows * D_MODEL * 2) / 1e6:.1f} MB",
                 "kernel": "gemm_i8_kernel (tcgen05 s8xs8->s32 + fused epilogue), five linears of a layer",
                 "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); nominal dense int8 4500",
                 "frac_of_nominal_4500": achieved / 4500.0,
@@ -397,6 +408,26 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return 0
+
+
+def run_only_gemms(pkg, rows, rounds):
+    import torch
+    dev = "cuda"
+    bufs = []
+    for name, n, k in LINEARS:
+        a8 = torch.randint(-127, 128, (rows, k), dtype=torch.int8, device=dev)
+        ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(rounds)]
+        sx, sw = torch.rand(rows, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-3
+        out = torch.empty(rows, n, dtype=torch.float32 if name == "up" else torch.float16, device=dev)
+        res = torch.randn(rows, n, device=dev).half() if n == D_MODEL else None
+        bufs.append((n, a8, ws, sx, sw, out, res, pkg.ACT_GELU_TANH if name == "up" else pkg.ACT_NONE))
+    for i in range(rounds):
+        for n, a8, ws, sx, sw, out, res, act in bufs:
+            pkg.linear(a8, sx, ws[i], sw, n=n, w_layout=pkg.W_SLAB128, residual=res, act=act, out=out,
+                       const_weights=True)
+    torch.cuda.synchronize()
+    print(json.dumps({"only_gemms_rows": rows, "rounds": rounds, "status": pkg.poll_status()}))
     return 0
 
 
