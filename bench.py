@@ -38,8 +38,10 @@ WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),
     "cfg2": (2048, 4, "bf16", 0),
-    "cfg3": (16384, 1, "fp16", 2048),   # 8 worlds x 2048 rows per GPU = the 64-world config on 8 GPUs
+    "cfg3": (None, 1, "fp16", 2048),    # 64 worlds x 2048 rows dealt over the ranks (strong scaling)
 }
+CFG3_WORLDS, CFG3_ROWS_PER_WORLD = 64, 2048
+SKINNY_SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048)]  # (K, N) of config 4
 
 
 def _load(name, path):
@@ -313,12 +315,19 @@ def main():
         return run_only_gemms(pkg, args.only_gemms, max(args.steps, 1))
     peaks = measured_peaks()
     rows, chained, dt_name, band = WORKLOADS[args.workload]
+    sharding = _load("w8a8_sharding", ROOT / "worldmodel.cu_b200" / "sharding.py")
+    my_worlds = [rank]  # weak scaling: one independent world per rank, seeded by its global id
+    if args.workload == "cfg3":
+        my_worlds = sharding.world_seeds(CFG3_WORLDS, world, rank)
+        rows = len(my_worlds) * CFG3_ROWS_PER_WORLD
     dtype = torch.float16 if dt_name == "fp16" else torch.bfloat16
     use_graph = not args.no_graph
 
-    stack, setup_s = build_stack(pkg, ref, max(rows, 2048 if not args.no_extras else rows), band, dtype, args.layers)
-    # every rank = one independent world: its own seeded tokens, replicated weights
-    x = ref.make_tokens(rows, rank, dtype).to("cuda")
+    want_extras = not args.no_extras and world == 1 and args.workload == "cfg1" and args.layers == N_LAYERS
+    stack, setup_s = build_stack(pkg, ref, max(rows, 2048 if want_extras else rows), band, dtype, args.layers)
+    # every world has its own seeded tokens; weights are replicated on every rank
+    per_world = rows // len(my_worlds)
+    x = torch.cat([ref.make_tokens(per_world, w, dtype) for w in my_worlds]).to("cuda")
     y = torch.empty_like(x)
     stream = torch.cuda.Stream()
     step = lambda: stack.forward(x, y, steps=chained, use_graph=use_graph, stream=stream.cuda_stream)
@@ -338,7 +347,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ops_per_step = rows * OPS_PER_ROW_LAYER * args.layers * chained
-    value = world * ops_per_step * args.steps / (ms * 1e-3) / 1e12
+    total_rows = rows * world if args.workload != "cfg3" else CFG3_WORLDS * CFG3_ROWS_PER_WORLD
+    job_ops_per_step = total_rows * OPS_PER_ROW_LAYER * args.layers * chained
+    value = job_ops_per_step * args.steps / (ms * 1e-3) / 1e12
     launches = stack.launches_per_forward * args.steps
 
     # end to end through the host-buffer entry point (pinned host tokens in, pinned result out)
@@ -357,7 +368,7 @@ def main():
         t = torch.tensor([e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e_ms = float(t.item())
-    e2e_value = world * ops_per_step * args.steps / (e_ms * 1e-3) / 1e12
+    e2e_value = job_ops_per_step * args.steps / (e_ms * 1e-3) / 1e12
     io_bytes = rows * D_MODEL * 2
 
     if rank != 0:
@@ -389,7 +400,8 @@ def main():
 
     line = {"metric": "w8a8_linear_stack_int8_tops", "value": value, "unit": "TOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+            "scaling": "strong" if args.workload == "cfg3" else "weak", "vs_baseline": None, "dtype": "s8",
+            "data": "synthetic",
             "config": {"workload": f"{args.workload}: {args.layers}-layer W8A8 linear stack, M={rows} rows per GPU, "
                                    f"{chained} chained pass(es) per step, d=2048, qkv 6144, mlp 8192, {dt_name}",
                        "rows_per_gpu": rows, "layers": args.layers, "graph_replay": use_graph,
@@ -399,7 +411,7 @@ def main():
                     "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
             "roofline": roofline}
 
-    if not args.no_extras and world == 1 and args.workload == "cfg1" and args.layers == N_LAYERS:
+    if want_extras:
         line["extras"] = run_extras(pkg, ref, stack, stream, peaks)
     sampler.stop()
     if not args.no_cpu_baseline and world == 1:
@@ -459,6 +471,41 @@ def run_extras(pkg, ref, stack, stream, peaks):
             fn()
     ms, _, _ = time_steps(fn, 20, stream, lambda: None)
     out["cfg1_eager_ms_per_step"] = ms / 20
+    out["cfg4_skinny"] = run_skinny(pkg, stream, peaks)
+    return out
+
+
+def run_skinny(pkg, stream, peaks, n_weights=72):
+    """Config 4: M in {16, 128} rows against K x N int8 weights; a graph-replayed chain of 72 launches
+    with 72 distinct weight matrices (1.2 GB, far beyond L2); reports weight bytes per second."""
+    import torch
+    dev = "cuda"
+    out = {}
+    for k, n in SKINNY_SHAPES:
+        ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(n_weights)]
+        sw = torch.rand(n, device=dev) * 1e-3
+        for m in (16, 128):
+            a8 = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+            sx = torch.rand(m, device=dev) * 1e-2
+            y = torch.empty(m, n, dtype=torch.float16, device=dev)
+
+            def run():
+                for w in ws:
+                    pkg.linear(a8, sx, w, sw, n=n, w_layout=pkg.W_SLAB128, out=y, const_weights=True)
+            with torch.cuda.stream(stream):
+                run()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                run()
+            with torch.cuda.stream(stream):
+                graph.replay()
+            ms, _, _ = time_steps(graph.replay, 3, stream, lambda: None)
+            us = ms / (3 * n_weights) * 1e3
+            gbs = (n * k + m * k + 2 * m * n) / us / 1e3
+            out[f"m{m}_k{k}_n{n}"] = {"us_per_linear": us, "gb_per_s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                      "frac_of_8000": gbs / 8000.0}
+        del ws
     return out
 
 

@@ -115,10 +115,11 @@ void b200_w8a8_set_tile_width(int bn);
  * stream is still finishing, and waits on the device before it touches dependent data; off
  * gives classic full serialization, for A/B timing.  No counterpart in the reference. */
 void b200_w8a8_set_overlapped_launch(int on);
-/* Tuning aid: when dev_buf is non-NULL every later GEMM launch writes 8 nanosecond
- * timestamps per CTA (entry, pipeline start, first operands landed, last MMA issued,
- * first accumulator ready, last epilogue done, exit, unused) into the device buffer
- * dev_buf[grid][8] of uint64.  NULL switches it off.  No counterpart in the reference. */
+/* Tuning aid: when dev_buf is non-NULL every later GEMM launch writes nanosecond timestamps
+ * per CTA (0 entry, 1 pipeline start, 2 first operands landed, 3 last MMA issued, 4 first
+ * accumulator ready, 5 last epilogue done, 6 exit, 8-10 cluster split-K phases) into the
+ * device buffer dev_buf[grid][16] of uint64.  NULL switches it off.  No counterpart in the
+ * reference. */
 void b200_w8a8_set_trace_buffer(void *dev_buf);
 
 /* One fused linear: y = store( residual + gate * act( acc * x_scales[r] * w_scales[c] + bias[c] ) )

@@ -182,3 +182,29 @@ def test_split_k_planner_reports_workspace(pkg):
     lib = pkg.lib()
     assert lib.b200_w8a8_linear_workspace_size(16, 65536, 64) > 0       # one tile, very long K: the planner splits
     assert lib.b200_w8a8_linear_workspace_size(16384, 2048, 6144) == 0  # plenty of tiles: no split
+
+
+@pytest.mark.parametrize("m,k,n", [(512, 8192, 2048), (512, 2048, 2048), (100, 1024, 520), (16, 2048, 2048),
+                                   (300, 512, 6144)])
+@pytest.mark.parametrize("bn,splits", [(256, 4), (256, 2), (128, 4), (128, 2), (64, 2)])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_cluster_split_k_linear_bit_exact(pkg, ref, m, k, n, bn, splits, out_dtype):
+    """K split over the CTAs of a thread-block cluster; partial sums meet in shared memory.
+    Needs no workspace and must give the same bits as the unsplit kernel and the oracle."""
+    g = torch.Generator().manual_seed(m + k + bn)
+    a, b = codes(m, k, 31), codes(n, k, 32)
+    sx = torch.rand(m, generator=g) * 0.05 + 0.01
+    sw = torch.rand(n, generator=g) * 2e-4 + 1e-5
+    bias = torch.randn(n, generator=g) * 0.1
+    res = torch.randn(m, n, generator=g).to(out_dtype)
+    want = ref.linear_w8a8(a, sx, b, sw, bias=bias, residual=res, out_dtype=out_dtype)
+    pkg.lib().b200_w8a8_set_tile_width(bn | (splits << 16) | (2 << 24))
+    try:
+        got = pkg.linear(a.to(DEV), sx.to(DEV), b.to(DEV), sw.to(DEV), bias=bias.to(DEV), residual=res.to(DEV),
+                         out_dtype=out_dtype)
+        assert pkg.poll_status() == 0
+        assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8))
+        acc = pkg.gemm_i8_i32(a.to(DEV), b.to(DEV))
+        assert torch.equal(acc.cpu(), ref.gemm_i8_i32(a, b))
+    finally:
+        pkg.lib().b200_w8a8_set_tile_width(0)

@@ -70,6 +70,7 @@ struct GemmParams {
     int num_m_blocks, num_n_blocks, num_tiles, num_k_blocks;
     int group_m;     // m-blocks per raster group (keeps a band of A resident in L2)
     int splits, kb_per_split, num_work;  // split-K: work item = (tile, K range); num_work = tiles * splits
+    int split_mode;                      // 1 = partials meet in the global workspace, 2 = in cluster shared memory
     int a_stage_bytes;                   // bytes one A load delivers (fewer than 16 KB when M < 128)
     int32_t *ws_partials;                // [splits][M][N] raw partial accumulators (split-K only)
     int *ws_counters;                    // [tiles] arrival tickets, zero between launches
@@ -91,7 +92,7 @@ struct GemmParams {
 };
 
 __device__ __forceinline__ void trace_mark(const GemmParams &p, int slot) {
-    if (p.trace) p.trace[(size_t)blockIdx.x * 8 + slot] = global_timer_ns();
+    if (p.trace) p.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
 }
 
 __device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &m_blk, int &n_blk);
@@ -344,7 +345,9 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const CUtens
     else if (row_live) store32_direct<OUT>(p, w, row, col0);
 }
 
-template <int BN, int OUT, bool GENERAL, bool SPLITK>
+// SPLITK: 0 = one CTA owns the whole K range of a tile; 1 = K split over CTAs that meet in a
+// global workspace; 2 = K split over the CTAs of a cluster that meet in shared memory.
+template <int BN, int OUT, bool GENERAL, int SPLITK>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
@@ -434,6 +437,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
         __syncwarp();  // the whole warp must reach the closing barrier together
+        if (SPLITK == 2) {
+            cluster_sync_all();
+            cluster_sync_all();
+        }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_i8(BM, BN);
@@ -470,6 +477,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
         __syncwarp();
+        if (SPLITK == 2) {
+            cluster_sync_all();
+            cluster_sync_all();
+        }
     } else {
         // Eight epilogue warps: two per TMEM sub-partition, each taking half of the columns,
         // so every SM sub-core has two warps to hide latencies with.
@@ -506,11 +517,77 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             ok = mbar_wait_bounded(&bar_tfull[b], tph, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!ok && SPLITK != 2) break;  // (in a cluster every thread still has to meet the cluster barriers)
             if (warp == 2 && lane == 0) trace_mark(p, 4);
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * BN + half * kCols);
-            if (SPLITK) {
+            if (SPLITK == 2) {
+                // Split-K inside a cluster: the `splits` CTAs of a cluster hold partial sums of the
+                // same tile.  CTA r reduces and finishes the column slice [r, r+1) * BN / splits:
+                // every CTA pushes the other slices of its partial into their owner's shared memory
+                // (the operand ring, idle by now), one cluster barrier later every owner adds what
+                // it received to its own accumulators and runs the fused epilogue.  No global
+                // scratch, no atomics; integer sums are exact in any order.
+                const uint32_t rank = cluster_cta_rank();
+                const int slice_cols = BN / p.splits;        // 32, 64 or 128
+                const int own_chunks = slice_cols / 32;
+                const uint32_t ring = smem_u32(smem);
+                cluster_sync_all();  // every CTA of the cluster has finished reading its operand ring
+                if (warp == 2 && lane == 0) trace_mark(p, 8);
+                if (ok) {
+#pragma unroll 1
+                    for (int c = 0; c < kChunks; ++c) {
+                        const int col_in_tile = half * kCols + c * 32;
+                        const uint32_t owner = (uint32_t)(col_in_tile / slice_cols);
+                        if (owner == rank) continue;
+                        uint32_t r[32];
+                        tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
+                        tmem_ld_wait();
+                        const uint32_t slot = rank < owner ? rank : rank - 1u;
+                        const int j = (col_in_tile - (int)owner * slice_cols) / 32;  // chunk within the owner's slice
+                        // Receive layout [slot][sub-partition][chunk][vector g][lane]: one store
+                        // instruction of the warp fills 512 contiguous bytes, and the owner's warp
+                        // of the same sub-partition reads them back lane for lane.
+                        const uint32_t off =
+                            (uint32_t)((((slot * 4 + sub) * own_chunks + j) * 8) * 512 + lane * 16);
+                        const uint32_t remote = cluster_map_shared(ring + off, owner);
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            st_shared_cluster_v4(remote + (uint32_t)(g * 512), r[4 * g], r[4 * g + 1], r[4 * g + 2],
+                                                 r[4 * g + 3]);
+                    }
+                }
+                if (warp == 2 && lane == 0) trace_mark(p, 9);
+                cluster_sync_all();  // all partial slices have landed in their owners
+                if (warp == 2 && lane == 0) trace_mark(p, 10);
+                if (ok) {
+#pragma unroll 1
+                    for (int j = half; j < own_chunks; j += 2) {
+                        const int col_in_tile = (int)rank * slice_cols + j * 32;
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * BN + col_in_tile), r);
+                        tmem_ld_wait();
+                        for (int slot = 0; slot < p.splits - 1; ++slot) {
+                            const uint8_t *src = smem + (((slot * 4 + sub) * own_chunks + j) * 8) * 512 + lane * 16;
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                const uint4 q = *reinterpret_cast<const uint4 *>(src + g * 512);
+                                r[4 * g + 0] += q.x;
+                                r[4 * g + 1] += q.y;
+                                r[4 * g + 2] += q.z;
+                                r[4 * g + 3] += q.w;
+                            }
+                        }
+                        const int col0 = n_blk * BN + col_in_tile;
+                        uint4 res[4];
+                        fetch_residual16<OUT>(p, row0 + lane, col0, res);
+                        epilogue_chunk<OUT, true>(p, &tm_out, stage, r, res, lane, row0, col0, row_scale, seq++);
+                    }
+                }
+                if (warp == 2 && lane == 0) trace_mark(p, 5);
+                break;  // a clustered launch gives every CTA exactly one work item
+            }
+            if (SPLITK == 1) {
                 // Split-K: this CTA holds one of `splits` partial sums of the tile.  Every CTA
                 // parks its raw int32 partial in the workspace and takes a ticket; the CTA that
                 // draws the last ticket adds the partials (integer sums: exact in any order)
@@ -683,7 +760,7 @@ int make_out_map(CUtensorMap *map, const void *base, int dtype, uint64_t cols, u
 
 struct DeviceInfo {
     int sms = 0;
-    bool attr_set[3][4][3] = {};
+    bool attr_set[3][4][4] = {};
 };
 DeviceInfo &device_info(int dev) {
     static DeviceInfo info[64];
@@ -694,13 +771,13 @@ DeviceInfo &device_info(int dev) {
     return d;
 }
 
-template <int BN, int OUT, bool GENERAL, bool SPLITK>
+template <int BN, int OUT, bool GENERAL, int SPLITK>
 int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
     using C = Cfg<BN>;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     DeviceInfo &di = device_info(dev);
-    constexpr int kVariant = SPLITK ? 2 : (GENERAL ? 1 : 0);
+    constexpr int kVariant = SPLITK == 2 ? 3 : (SPLITK == 1 ? 2 : (GENERAL ? 1 : 0));
     if (!di.attr_set[slot][OUT][kVariant]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -738,19 +815,27 @@ int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t strea
     memset(&tm_out, 0, sizeof(tm_out));
     if (p.tma_store && make_out_map(&tm_out, a.out, a.out_dtype, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldo))
         return 1;
-    const int grid = p.num_work < di.sms ? p.num_work : di.sms;
-    cudaError_t le = launch_kernel(gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>, dim3(grid), dim3(kThreads),
-                                   (size_t)C::kSmemBytes, stream, tm_a, tm_b, tm_out, p);
+    cudaError_t le;
+    if (SPLITK == 2) {
+        // one work item per CTA, `splits` consecutive CTAs form a cluster
+        le = launch_kernel_cluster(gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>, dim3(p.num_work), dim3(kThreads),
+                                   (size_t)C::kSmemBytes, stream, (unsigned)p.splits, tm_a, tm_b, tm_out, p);
+    } else {
+        const int grid = p.num_work < di.sms ? p.num_work : di.sms;
+        le = launch_kernel(gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>, dim3(grid), dim3(kThreads),
+                           (size_t)C::kSmemBytes, stream, tm_a, tm_b, tm_out, p);
+    }
     if (le != cudaSuccess) return fail("launching gemm_i8_tcgen05: %s", cudaGetErrorString(le));
     return check_launch("gemm_i8_tcgen05");
 }
 
 template <int BN, int OUT>
 int launch_bn(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
-    if (p.splits > 1) return launch_bn_g<BN, OUT, true, true>(a, p, slot, stream);
+    if (p.splits > 1 && p.split_mode == 2) return launch_bn_g<BN, OUT, true, 2>(a, p, slot, stream);
+    if (p.splits > 1) return launch_bn_g<BN, OUT, true, 1>(a, p, slot, stream);
     const bool lean = p.tma_store && p.vec_ok && (a.n % 32 == 0);
-    return lean ? launch_bn_g<BN, OUT, false, false>(a, p, slot, stream)
-                : launch_bn_g<BN, OUT, true, false>(a, p, slot, stream);
+    return lean ? launch_bn_g<BN, OUT, false, 0>(a, p, slot, stream)
+                : launch_bn_g<BN, OUT, true, 0>(a, p, slot, stream);
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -790,12 +875,15 @@ constexpr size_t kCounterBytes = 4096;  // ticket counters at the head of the wo
 struct Plan {
     int bn = 256;
     int splits = 1;
+    int mode = 0;  // 0 no split, 1 workspace split-K, 2 cluster split-K
 };
 
 // Picks the tile width and the K split from a small time model (microseconds).  A tile costs
-// its K slabs (bounded by the MMA rate and by how fast one SM can pull operands), its
-// epilogue and, when K is split, the partial-sum exchange; tiles run in waves over the SMs.
-Plan make_plan(int m, int k, int n, int sms, bool allow_split) {
+// its K slabs (bounded by the MMA rate and by how fast one SM can pull operands through L2),
+// its epilogue and, when K is split, the partial-sum exchange; tiles run in waves over the SMs.
+// Splitting K inside a cluster needs no scratch and costs two cluster barriers; splitting
+// through the global workspace costs fences and a serial read-back and only pays for very long K.
+Plan make_plan(int m, int k, int n, int sms, bool allow_workspace) {
     const int mb = (m + BM - 1) / BM;
     const int kblocks = (k + BK - 1) / BK;
     const double a_kb = (m >= BM ? BM : ((m + 15) / 16) * 16) * (double)BK / 1024.0;
@@ -805,22 +893,32 @@ Plan make_plan(int m, int k, int n, int sms, bool allow_split) {
     for (int wi = 0; wi < 3; ++wi) {
         const int bn = widths[wi];
         const long long tiles = (long long)mb * ((n + bn - 1) / bn);
-        const int max_splits = (allow_split && (n % 4) == 0 && tiles < sms && tiles <= 1024) ? 8 : 1;
-        for (int sp = 1; sp <= max_splits; ++sp) {
-            if (sp > 1 && kblocks / sp < 2) break;
-            const long long work = tiles * sp;
-            if (sp > 1 && work > sms) break;  // keep all partials of a launch in one wave
-            const int kbps = (kblocks + sp - 1) / sp;
-            const double waves = (double)((work + sms - 1) / sms);
-            const double t_mma = 0.065 * bn / 64.0;
-            const double t_load = (a_kb + bn * (double)BK / 1024.0) / 150.0;  // ~150 KB/us per SM
-            const double t_epi = 0.45 * bn / 64.0;
-            const double t_red = sp > 1 ? 3.0 + 1.0 * sp * bn / 64.0 : 0.0;  // measured: fences + serial partial reads
-            const double t = waves * (0.3 + kbps * (t_mma > t_load ? t_mma : t_load) + t_epi + t_red);
-            if (t < best_t) {
-                best_t = t;
-                best.bn = bn;
-                best.splits = sp;
+        for (int mode = 0; mode <= 2; ++mode) {
+            if (mode == 1 && !(allow_workspace && (n % 4) == 0 && tiles <= 1024)) continue;
+            const int max_splits = mode == 0 ? 1 : (mode == 2 ? 4 : 8);
+            for (int sp = (mode == 0 ? 1 : 2); sp <= max_splits; sp *= (mode == 2 ? 2 : 1), sp += (mode == 2 ? 0 : 1)) {
+                if (sp > 1 && kblocks / sp < 2) break;
+                if (mode == 2 && (bn / sp < 32 || kblocks % sp != 0)) break;
+                const long long work = tiles * sp;
+                if (sp > 1 && work > sms) break;  // keep all partials of a launch in one wave
+                const int kbps = (kblocks + sp - 1) / sp;
+                const double waves = (double)((work + sms - 1) / sms);
+                const double t_mma = 0.065 * bn / 64.0;
+                // one SM pulls ~150 KB/us through L2, but with ~100+ CTAs marching over the same
+                // A tiles a K slab has not been seen to take less than ~0.3 us (measured)
+                double t_load = (a_kb + bn * (double)BK / 1024.0) / 150.0;
+                if (work >= 64 && t_load < 0.30) t_load = 0.30;
+                const double t_epi = 0.45 * bn / 64.0 / (mode == 2 ? sp : 1);
+                // cluster exchange: (sp-1)/sp of a 128 x bn int32 tile per CTA at ~20 KB/us (measured)
+                const double t_red = mode == 1 ? 3.0 + 1.0 * sp * bn / 64.0
+                                               : (mode == 2 ? 1.0 + (sp - 1.0) / sp * bn * 0.0256 : 0.0);
+                const double t = waves * (0.3 + kbps * (t_mma > t_load ? t_mma : t_load) + t_epi + t_red);
+                if (t < best_t) {
+                    best_t = t;
+                    best.bn = bn;
+                    best.splits = sp;
+                    best.mode = mode;
+                }
             }
         }
     }
@@ -839,7 +937,7 @@ int device_sms() {
 size_t gemm_workspace_size(int m, int k, int n) {
     if (m <= 0 || k <= 0 || n <= 0) return 0;
     const Plan pl = make_plan(m, k, n, device_sms(), true);
-    return pl.splits > 1 ? kCounterBytes + (size_t)pl.splits * (size_t)m * (size_t)n * sizeof(int32_t) : 0;
+    return pl.mode == 1 ? kCounterBytes + (size_t)pl.splits * (size_t)m * (size_t)n * sizeof(int32_t) : 0;
 }
 
 namespace {
@@ -870,25 +968,37 @@ int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_byte
 
     const bool ws_ok = workspace && aligned16(workspace);
     Plan pl = make_plan(a.m, a.k, a.n, device_sms(), ws_ok);
-    int force_bn = g_force_bn & 0xFFFF, force_splits = g_force_bn >> 16;
+    int force_bn = g_force_bn & 0xFFFF, force_splits = (g_force_bn >> 16) & 0xFF, force_mode = g_force_bn >> 24;
     if (fixed_plan) {
         force_bn = fixed_plan->bn;
         force_splits = fixed_plan->splits;
+        force_mode = fixed_plan->mode;
     }
     if (force_bn == 256 || force_bn == 128 || force_bn == 64) pl.bn = force_bn;
-    if (force_splits >= 1) pl.splits = force_splits;
-    if (pl.splits > 1) {
+    if (force_splits >= 1) {
+        pl.splits = force_splits;
+        pl.mode = force_splits == 1 ? 0 : (force_mode == 2 ? 2 : 1);
+    }
+    if (pl.mode == 2) {
+        const int kblocks = (a.k + BK - 1) / BK;
+        if (pl.bn / pl.splits < 32 || kblocks % pl.splits != 0 || pl.splits > 8)
+            return fail("cluster split-K needs BN/splits >= 32 and K blocks divisible by splits (bn=%d splits=%d)",
+                        pl.bn, pl.splits);
+    }
+    if (pl.mode == 1) {
         const size_t need = kCounterBytes + (size_t)pl.splits * (size_t)a.m * (size_t)a.n * sizeof(int32_t);
         const long long tiles = (long long)((a.m + BM - 1) / BM) * ((a.n + pl.bn - 1) / pl.bn);
         if (!ws_ok || workspace_bytes < need || tiles > 1024 || (a.n % 4) != 0) {
             if (force_splits > 1) return fail("split-K needs %zu bytes of workspace, got %zu", need, workspace_bytes);
             pl = make_plan(a.m, a.k, a.n, device_sms(), false);
+            if (force_bn == 256 || force_bn == 128 || force_bn == 64) pl.bn = force_bn;
         } else {
             p.ws_counters = reinterpret_cast<int *>(workspace);
             p.ws_partials = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(workspace) + kCounterBytes);
         }
     }
     p.splits = pl.splits;
+    p.split_mode = pl.mode;
 #define B200_LAUNCH(BN_, SLOT_)                                                       \
     switch (a.out_dtype) {                                                            \
         case B200_DT_S32: return launch_bn<BN_, B200_DT_S32>(a, p, SLOT_, stream);    \
@@ -930,7 +1040,12 @@ int linear_static_scratch(const LinearArgs &a, cudaStream_t stream) {
     if (kblocks < 4 || (a.n % 4) != 0)
         return fail("the no-allocation linear needs K >= 512 and N %% 4 == 0, got K=%d N=%d", a.k, a.n);
     Plan pl = make_plan(a.m, a.k, a.n, device_sms(), true);
-    if (pl.splits < 2) pl.splits = 2;
+    if (pl.mode != 1) {
+        pl = Plan();
+        pl.bn = a.m <= 128 ? 64 : 128;
+        pl.splits = 2;
+    }
+    pl.mode = 1;  // this entry point is the workspace form of split-K by definition
     const long long tiles = (long long)((a.m + BM - 1) / BM) * ((a.n + pl.bn - 1) / pl.bn);
     const size_t need = kCounterBytes + (size_t)pl.splits * (size_t)a.m * (size_t)a.n * sizeof(int32_t);
     if (need > kStaticScratchBytes || tiles > 1024)
