@@ -139,3 +139,23 @@ def test_qkv_rms_rope_dequant(pkg, ref):
     assert torch.equal(v.cpu(), v_ref)  # plain dequant: exact
     assert torch.allclose(q.cpu(), q_ref, rtol=1e-5, atol=2e-6)  # cos/sin differ in the last ulps
     assert torch.allclose(k.cpu(), k_ref, rtol=1e-5, atol=2e-6)
+
+
+def test_quantize_rows_many_scales_bit_exact(pkg, ref):
+    """The kernel divides by the row scale with a refined reciprocal multiply instead of a division
+    instruction; that must still be the correctly rounded quotient for every scale.  65536 rows with
+    scales over 60 binades, values placed at and next to rounding ties, plus tiny and huge rows."""
+    g = torch.Generator().manual_seed(99)
+    rows, cols = 65536, 64
+    amax = torch.exp2(torch.rand(rows, generator=g) * 60 - 30) * (1 + torch.rand(rows, generator=g))
+    codes = torch.randint(-127, 128, (rows, cols), generator=g).float()
+    frac = torch.tensor([0.0, 0.5, -0.5, 0.49999997, 0.50000006, 0.25, -0.49999997, 0.5])[
+        torch.randint(0, 8, (rows, cols), generator=g)]
+    x = (codes + frac) * (amax / 127.0)[:, None]
+    x[:, 0] = amax
+    x[:16] *= 1e-35   # near the subnormal range: the plain-division path
+    x[16:32] *= 1e30
+    q_ref, s_ref = ref.quantize_rows(x)
+    q, s = pkg.quantize_rows(x.to(DEV))
+    assert torch.equal(bits(s), bits(s_ref))
+    assert torch.equal(q.cpu(), q_ref)

@@ -201,6 +201,31 @@ __device__ __forceinline__ int quantize_code(float v, float scale) {
     int q = __float2int_rn(__fdiv_rn(v, scale));
     return max(-127, min(127, q));
 }
+// The same code without a per-element reciprocal or float->int conversion (both run on the
+// 16-lane special-function unit and made the quantizers compute-bound).  The row's scale is
+// inverted once, correctly rounded; q = RN(x*y), r = x - q*s (exact in an FMA), q' = RN(q + r*y)
+// is then the correctly rounded quotient x / s (Markstein's division step), i.e. bit-identical
+// to __fdiv_rn.  Rounding to the nearest-even integer is one add of 1.5 * 2^23, whose low
+// mantissa bits are the integer.  Rows whose scale is tiny enough for 1/s to overflow take the
+// plain division.
+struct RowScale {
+    float scale;
+    float inv;   // RN(1 / scale), or 0 when the slow path must be used
+};
+__device__ __forceinline__ RowScale make_row_scale(float amax) {
+    RowScale r;
+    r.scale = absmax_to_scale(amax);
+    r.inv = (r.scale > 1e-30f && r.scale < 1e30f) ? __frcp_rn(r.scale) : 0.0f;
+    return r;
+}
+__device__ __forceinline__ int quantize_code(float v, const RowScale &rs) {
+    if (rs.inv == 0.0f) return quantize_code(v, rs.scale);
+    const float q0 = __fmul_rn(v, rs.inv);
+    const float rem = __fmaf_rn(-q0, rs.scale, v);
+    const float q = __fmaf_rn(rem, rs.inv, q0);
+    const int c = __float_as_int(__fadd_rn(q, 12582912.0f)) - 0x4B400000;
+    return max(-127, min(127, c));
+}
 __device__ __forceinline__ float dequant_acc(int acc, float row_scale, float col_scale) {
     return __fmul_rn(__fmul_rn((float)acc, row_scale), col_scale);
 }

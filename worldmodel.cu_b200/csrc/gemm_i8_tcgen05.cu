@@ -273,20 +273,36 @@ template <int OUT>
 __device__ __forceinline__ void stage_and_store(const GemmParams &p, const CUtensorMap *tm_out, uint8_t *stage,
                                                 const uint32_t (&w)[32], int lane, int row0, int col0, int seq) {
     constexpr bool k32 = (OUT == B200_DT_S32 || OUT == B200_DT_F32);
-    // 32-bit: one 4 KB block, must be drained before reuse.  16-bit: two 2 KB blocks, alternate.
-    uint8_t *buf = k32 ? stage : stage + (seq & 1) * 2048;
-    if (lane == 0) {
-        if (k32) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-    }
-    __syncwarp();
+    // The warp owns two 2 KB staging blocks of 32 rows x 64 bytes (64-byte swizzle) and alternates
+    // between them, so one bulk store can drain while the next block is being filled.  A 16-bit
+    // chunk (32 columns) is one block; a 32-bit chunk is two blocks of 16 columns.
     if (k32) {
-        uint8_t *rowp = buf + lane * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4 *>(rowp + ((c ^ (lane & 7)) << 4)) =
-                make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-    } else {
+        for (int h = 0; h < 2; ++h) {
+            uint8_t *buf = stage + h * 2048;
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            uint8_t *rowp = buf + lane * 64;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4 *>(rowp + ((c ^ ((lane >> 1) & 3)) << 4)) =
+                    make_uint4(w[16 * h + 4 * c], w[16 * h + 4 * c + 1], w[16 * h + 4 * c + 2], w[16 * h + 4 * c + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                                 tm_out),
+                             "r"(col0 + 16 * h), "r"(row0), "r"(smem_u32(buf))
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+        }
+        return;
+    }
+    uint8_t *buf = stage + (seq & 1) * 2048;
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    __syncwarp();
+    {
         constexpr int O = Out16<OUT>::value;
         uint8_t *rowp = buf + lane * 64;
 #pragma unroll
@@ -739,8 +755,8 @@ int make_map(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint6
     return 0;
 }
 
-// Output matrix [rows, cols] of 16- or 32-bit elements, written in 32 x 32 blocks whose
-// shared-memory image uses the swizzle that makes a row-per-thread write conflict-free.
+// Output matrix [rows, cols] of 16- or 32-bit elements, written in blocks of 32 rows x 64 bytes
+// whose shared-memory image uses the swizzle that makes a row-per-thread write conflict-free.
 int make_out_map(CUtensorMap *map, const void *base, int dtype, uint64_t cols, uint64_t rows, uint64_t ld) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
@@ -748,12 +764,11 @@ int make_out_map(CUtensorMap *map, const void *base, int dtype, uint64_t cols, u
     const uint64_t esz = k32 ? 4 : 2;
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {ld * esz};
-    cuuint32_t box[2] = {32, 32};
+    cuuint32_t box[2] = {k32 ? 16u : 32u, 32};  // 64-byte rows either way
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, k32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
                     const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    k32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled (output) failed (%d)", (int)r);
     return 0;
 }

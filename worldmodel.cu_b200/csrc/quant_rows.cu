@@ -225,8 +225,8 @@ __global__ void __launch_bounds__(kThreads) quant_rows_vec_kernel(QuantArgs a) {
         }
     }
     amax = group_max<G>(amax, red_f);
-    const float scale = absmax_to_scale(amax);
-    if (live && gl == 0) a.scales[row] = scale;
+    const RowScale scale = make_row_scale(amax);
+    if (live && gl == 0) a.scales[row] = scale.scale;
 
     int8_t *qrow = a.q + (long long)row * a.ldq;
 #pragma unroll
@@ -283,9 +283,9 @@ __global__ void __launch_bounds__(kThreads) quant_rows_any_kernel(QuantArgs a) {
     float amax = 0.0f;
     for (int c = threadIdx.x; c < a.cols; c += kThreads) amax = fmaxf(amax, fabsf(value(c)));
     amax = group_max<kThreads>(amax, red_f);
-    const float scale = absmax_to_scale(amax);
+    const RowScale scale = make_row_scale(amax);
     __syncthreads();  // every thread has read in_row_scales[row] before it may be overwritten
-    if (threadIdx.x == 0) a.scales[row] = scale;
+    if (threadIdx.x == 0) a.scales[row] = scale.scale;
     int8_t *qrow = a.q + (long long)row * a.ldq;
     for (int c = threadIdx.x; c < a.cols; c += kThreads) qrow[c] = (int8_t)quantize_code(value(c), scale);
 }
