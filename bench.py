@@ -38,7 +38,7 @@ WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),
     "cfg2": (2048, 4, "bf16", 0),
-    "cfg3": (None, 1, "fp16", 2048),    # 64 worlds x 2048 rows dealt over the ranks (strong scaling)
+    "cfg3": (None, 1, "fp16", 4096),    # 64 worlds x 2048 rows dealt over the ranks (strong scaling)
 }
 CFG3_WORLDS, CFG3_ROWS_PER_WORLD = 64, 2048
 SKINNY_SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048)]  # (K, N) of config 4
@@ -287,6 +287,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configs reported under `extras`")
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers of the stack (24 = the real workload)")
+    ap.add_argument("--band", type=int, default=-1, help="rows per band (default: the workload's own)")
+    ap.add_argument("--lanes", type=int, default=0, help="streams that bands alternate over (default 2 for cfg3)")
     ap.add_argument("--only-gemms", type=int, default=0, metavar="ROWS",
                     help="run the five fused linears of one layer at ROWS rows for --steps rounds with distinct "
                          "weights and exit (a small, self-ending case for ncu captures)")
@@ -322,9 +324,13 @@ def main():
         rows = len(my_worlds) * CFG3_ROWS_PER_WORLD
     dtype = torch.float16 if dt_name == "fp16" else torch.bfloat16
     use_graph = not args.no_graph
+    if args.band >= 0:
+        band = args.band
+    lanes = args.lanes if args.lanes > 0 else (2 if args.workload == "cfg3" else 1)
 
     want_extras = not args.no_extras and world == 1 and args.workload == "cfg1" and args.layers == N_LAYERS
     stack, setup_s = build_stack(pkg, ref, max(rows, 2048 if want_extras else rows), band, dtype, args.layers)
+    stack.set_lanes(lanes)
     # every world has its own seeded tokens; weights are replicated on every rank
     per_world = rows // len(my_worlds)
     x = torch.cat([ref.make_tokens(per_world, w, dtype) for w in my_worlds]).to("cuda")
@@ -405,6 +411,7 @@ def main():
             "config": {"workload": f"{args.workload}: {args.layers}-layer W8A8 linear stack, M={rows} rows per GPU, "
                                    f"{chained} chained pass(es) per step, d=2048, qkv 6144, mlp 8192, {dt_name}",
                        "rows_per_gpu": rows, "layers": args.layers, "graph_replay": use_graph,
+                       "band_rows": band, "lanes": lanes,
                        "l2": "no flush: each step streams 1.31 GB of int8 weights, 10x the 126 MB L2"},
             "gpu_launches": int(launches), "clocks": clocks, "setup_s": setup_s,
             "e2e": {"value": e2e_value, "unit": "TOP/s", "ms_per_step": e_ms / args.steps,

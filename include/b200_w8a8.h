@@ -207,6 +207,12 @@ int b200_w8a8_stack_forward(void *stack, const void *x_dev, void *y_dev, int row
 /* Same with HOST buffers (pinned for full speed): copies in, runs, copies out, and
  * returns after the result has landed. */
 int b200_w8a8_stack_forward_host(void *stack, const void *x_host, void *y_host, int rows, int steps, int use_graph);
+/* lanes = 2 runs alternate bands of rows on two streams (a second scratch set is allocated once),
+ * so the bandwidth-bound quantizers of one band overlap the tensor-bound GEMMs of the other.
+ * Only has an effect when a forward covers at least two bands.  The reference runs everything on
+ * one stream (CMakeLists.txt:46); rows of different bands never interact, so results are
+ * unchanged. */
+int b200_w8a8_stack_set_lanes(void *stack, int lanes);
 /* Switches the 16-bit activation type (fp16 <-> bf16) of later forwards; both are 2 bytes,
  * so buffers are kept and only cached graphs are dropped. */
 int b200_w8a8_stack_set_act_dtype(void *stack, int act_dtype);

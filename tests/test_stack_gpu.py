@@ -70,14 +70,16 @@ def test_each_operator_of_a_layer_against_the_oracle_on_the_same_inputs(pkg, ref
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("rows,band,steps,graph", [(200, 0, 1, False), (200, 128, 2, False), (333, 0, 2, True),
-                                                   (16, 0, 1, True)])
-def test_stack_driver_equals_operator_composition(pkg, ref, dtype, rows, band, steps, graph):
+@pytest.mark.parametrize("rows,band,steps,graph,lanes", [(200, 0, 1, False, 1), (200, 128, 2, False, 1),
+                                                         (333, 0, 2, True, 1), (16, 0, 1, True, 1),
+                                                         (333, 64, 1, False, 2), (333, 96, 2, True, 2)])
+def test_stack_driver_equals_operator_composition(pkg, ref, dtype, rows, band, steps, graph, lanes):
     n_layers = 3
     layers_fp32 = [ref.make_layer_fp32(l, D, NQKV, HID) for l in range(n_layers)]
     stack = pkg.LinearStack(D, NQKV, HID, n_layers, max_rows=rows, band_rows=band, dtype=dtype)
     for l, (ws, gs) in enumerate(layers_fp32):
         stack.set_layer(l, ws, gs, threads=4)
+    stack.set_lanes(lanes)  # two lanes: alternate bands run on two streams
     Ls = [dev_layer(pkg, ref.make_layer(l, D, NQKV, HID)) for l in range(n_layers)]
     x = ref.make_tokens(rows, 1, dtype, D).to(DEV)
     want = x

@@ -62,6 +62,7 @@ _PROTOTYPES = {
     "b200_w8a8_stack_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_stack_forward_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "b200_w8a8_stack_set_act_dtype": (c_int, [c_void_p, c_int]),
+    "b200_w8a8_stack_set_lanes": (c_int, [c_void_p, c_int]),
     "b200_w8a8_stack_device_bytes": (c_size_t, [c_void_p]),
     "b200_w8a8_stack_launches_per_forward": (ctypes.c_longlong, [c_void_p]),
 }
@@ -271,6 +272,9 @@ class LinearStack:
         _check(lib().b200_w8a8_stack_forward_host(self.handle, x_host.data_ptr(), y_host.data_ptr(), x_host.shape[0],
                                                   steps, int(use_graph)), "stack_forward_host")
         return y_host
+
+    def set_lanes(self, lanes):
+        _check(lib().b200_w8a8_stack_set_lanes(self.handle, lanes), "stack_set_lanes")
 
     def set_dtype(self, dtype):
         import torch

@@ -226,6 +226,21 @@ __device__ __forceinline__ int quantize_code(float v, const RowScale &rs) {
     const int c = __float_as_int(__fadd_rn(q, 12582912.0f)) - 0x4B400000;
     return max(-127, min(127, c));
 }
+// For packing: the float 1.5*2^23 + code, whose lowest mantissa byte is the two's-complement
+// int8 code itself (|code| <= 127 always holds for finite inputs: |v| <= amax and
+// scale >= RN(amax/127) bound the quotient by 127.00001).  Four such floats become one word of
+// codes with three byte permutes.
+__device__ __forceinline__ float quantize_biased(float v, const RowScale &rs) {
+    if (rs.inv == 0.0f) return __int_as_float(0x4B400000 + quantize_code(v, rs.scale));
+    const float q0 = __fmul_rn(v, rs.inv);
+    const float rem = __fmaf_rn(-q0, rs.scale, v);
+    return __fadd_rn(__fmaf_rn(rem, rs.inv, q0), 12582912.0f);
+}
+__device__ __forceinline__ uint32_t pack_biased4(float t0, float t1, float t2, float t3) {
+    const uint32_t lo = __byte_perm(__float_as_uint(t0), __float_as_uint(t1), 0x0040);
+    const uint32_t hi = __byte_perm(__float_as_uint(t2), __float_as_uint(t3), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
 __device__ __forceinline__ float dequant_acc(int acc, float row_scale, float col_scale) {
     return __fmul_rn(__fmul_rn((float)acc, row_scale), col_scale);
 }

@@ -43,10 +43,17 @@ struct Stack {
     std::vector<Layer> layers;
     // full-height token buffers (residual stream) and band-height scratch
     void *tok[3] = {nullptr, nullptr, nullptr};
-    int8_t *a8 = nullptr;       // [band, max(d, hidden)]
-    float *a8_scales = nullptr; // [band]
-    void *qkv = nullptr;        // [band, n_qkv] 16-bit
-    float *h = nullptr;         // [band, hidden] fp32 hidden before re-quantization
+    // band-height scratch, one set per lane: bands are independent (rows never interact), so two
+    // lanes on two streams let one band's bandwidth-bound quantizers run under the other band's GEMMs
+    struct Scratch {
+        int8_t *a8 = nullptr;        // [band, max(d, hidden)]
+        float *a8_scales = nullptr;  // [band]
+        void *qkv = nullptr;         // [band, n_qkv] 16-bit
+        float *h = nullptr;          // [band, hidden] fp32 hidden before re-quantization
+    } scratch[2];
+    int lanes = 1;
+    cudaStream_t lane_stream = nullptr;   // stream of the second lane
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     void *host_stage = nullptr; // device staging for the host entry point
     void *host_out = nullptr;
     cudaStream_t own_stream = nullptr;
@@ -99,20 +106,21 @@ int fused(const Stack *s, const Weight &w, const int8_t *a8, const float *a8_sca
     return gemm_launch(a, nullptr, 0, stream);
 }
 
-// The ten operators of one layer on rows [r0, r0+rows) of the residual stream.
-int layer_band(Stack *s, const Layer &L, const void *x, void *x1, void *x2, void *x3, int rows, cudaStream_t st) {
+// The ten operators of one layer on one band of rows of the residual stream.
+int layer_band(Stack *s, const Stack::Scratch &w, const Layer &L, const void *x, void *x1, void *x2, void *x3,
+               int rows, cudaStream_t st) {
     const int d = s->d, dt = s->dtype;
-    if (rms_norm_quantize_rows(x, dt, d, L.g_attn, 0, nullptr, s->a8, d, s->a8_scales, rows, d, s->eps, st)) return 1;
-    if (fused(s, L.qkv, s->a8, s->a8_scales, nullptr, B200_ACT_NONE, s->qkv, dt, s->n_qkv, rows, st)) return 1;
-    if (quantize_rows(s->qkv, dt, s->n_qkv, s->a8, d, s->a8_scales, rows, d, st)) return 1;
-    if (fused(s, L.out, s->a8, s->a8_scales, x, B200_ACT_NONE, x1, dt, d, rows, st)) return 1;
-    if (rms_norm_quantize_rows(x1, dt, d, L.g_ctrl, 0, nullptr, s->a8, d, s->a8_scales, rows, d, s->eps, st)) return 1;
-    if (fused(s, L.ctrl, s->a8, s->a8_scales, x1, B200_ACT_NONE, x2, dt, d, rows, st)) return 1;
-    if (rms_norm_quantize_rows(x2, dt, d, L.g_mlp, 0, nullptr, s->a8, d, s->a8_scales, rows, d, s->eps, st)) return 1;
-    if (fused(s, L.up, s->a8, s->a8_scales, nullptr, B200_ACT_GELU_TANH, s->h, B200_DT_F32, s->hidden, rows, st))
+    if (rms_norm_quantize_rows(x, dt, d, L.g_attn, 0, nullptr, w.a8, d, w.a8_scales, rows, d, s->eps, st)) return 1;
+    if (fused(s, L.qkv, w.a8, w.a8_scales, nullptr, B200_ACT_NONE, w.qkv, dt, s->n_qkv, rows, st)) return 1;
+    if (quantize_rows(w.qkv, dt, s->n_qkv, w.a8, d, w.a8_scales, rows, d, st)) return 1;
+    if (fused(s, L.out, w.a8, w.a8_scales, x, B200_ACT_NONE, x1, dt, d, rows, st)) return 1;
+    if (rms_norm_quantize_rows(x1, dt, d, L.g_ctrl, 0, nullptr, w.a8, d, w.a8_scales, rows, d, s->eps, st)) return 1;
+    if (fused(s, L.ctrl, w.a8, w.a8_scales, x1, B200_ACT_NONE, x2, dt, d, rows, st)) return 1;
+    if (rms_norm_quantize_rows(x2, dt, d, L.g_mlp, 0, nullptr, w.a8, d, w.a8_scales, rows, d, s->eps, st)) return 1;
+    if (fused(s, L.up, w.a8, w.a8_scales, nullptr, B200_ACT_GELU_TANH, w.h, B200_DT_F32, s->hidden, rows, st))
         return 1;
-    if (quantize_rows(s->h, B200_DT_F32, s->hidden, s->a8, s->hidden, s->a8_scales, rows, s->hidden, st)) return 1;
-    if (fused(s, L.down, s->a8, s->a8_scales, x2, B200_ACT_NONE, x3, dt, d, rows, st)) return 1;
+    if (quantize_rows(w.h, B200_DT_F32, s->hidden, w.a8, s->hidden, w.a8_scales, rows, s->hidden, st)) return 1;
+    if (fused(s, L.down, w.a8, w.a8_scales, x2, B200_ACT_NONE, x3, dt, d, rows, st)) return 1;
     return 0;
 }
 
@@ -120,8 +128,19 @@ int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t 
     const size_t row_bytes = (size_t)s->d * esize(s->dtype);
     const int total_layers = steps * s->n_layers;
     long long launches = 0;
-    for (int r0 = 0; r0 < rows; r0 += s->band_rows) {
+    const int n_bands = (rows + s->band_rows - 1) / s->band_rows;
+    const bool two_lanes = s->lanes == 2 && n_bands >= 2;
+    if (two_lanes) {  // the second lane starts after everything already queued on the caller's stream
+        if (cudaEventRecord(s->ev_fork, st) != cudaSuccess ||
+            cudaStreamWaitEvent(s->lane_stream, s->ev_fork, 0) != cudaSuccess)
+            return fail("forking the second lane failed");
+    }
+    int band = 0;
+    for (int r0 = 0; r0 < rows; r0 += s->band_rows, ++band) {
         const int nr = rows - r0 < s->band_rows ? rows - r0 : s->band_rows;
+        const int lane = two_lanes ? (band & 1) : 0;
+        cudaStream_t bst = lane ? s->lane_stream : st;
+        const Stack::Scratch &w = s->scratch[lane];
         const size_t off = (size_t)r0 * row_bytes;
         const void *cur = (const char *)x + off;
         int cur_slot = -1;  // -1: caller's input
@@ -138,13 +157,28 @@ int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t 
             const int x3_slot = cur_slot >= 0 ? cur_slot : free_slots[2];
             const bool last = li == total_layers - 1;
             void *x3 = last ? (char *)y + off : (char *)s->tok[x3_slot] + off;
-            if (layer_band(s, L, cur, x1, x2, x3, nr, st)) return 1;
+            if (layer_band(s, w, L, cur, x1, x2, x3, nr, bst)) return 1;
             launches += 10;
             cur = x3;
             cur_slot = x3_slot;
         }
     }
+    if (two_lanes) {  // the caller's stream continues only when the second lane is done
+        if (cudaEventRecord(s->ev_join, s->lane_stream) != cudaSuccess ||
+            cudaStreamWaitEvent(st, s->ev_join, 0) != cudaSuccess)
+            return fail("joining the second lane failed");
+    }
     s->launches_per_forward = launches;
+    return 0;
+}
+
+int alloc_scratch(Stack *s, Stack::Scratch *w) {
+    const size_t e = esize(s->dtype);
+    const int wide = s->hidden > s->d ? s->hidden : s->d;
+    if (dev_alloc(s, (void **)&w->a8, (size_t)s->band_rows * wide)) return 1;
+    if (dev_alloc(s, (void **)&w->a8_scales, (size_t)s->band_rows * sizeof(float))) return 1;
+    if (dev_alloc(s, &w->qkv, (size_t)s->band_rows * s->n_qkv * e)) return 1;
+    if (dev_alloc(s, (void **)&w->h, (size_t)s->band_rows * s->hidden * sizeof(float))) return 1;
     return 0;
 }
 
@@ -173,13 +207,9 @@ void *b200_w8a8_stack_create(int d_model, int n_qkv, int d_hidden, int n_layers,
     s->layers.resize((size_t)n_layers);
     cudaGetDevice(&s->device);
     const size_t e = esize(act_dtype);
-    const int wide = d_hidden > d_model ? d_hidden : d_model;
     bool ok = true;
     for (int i = 0; i < 3 && ok; ++i) ok = !dev_alloc(s, &s->tok[i], (size_t)max_rows * d_model * e);
-    ok = ok && !dev_alloc(s, (void **)&s->a8, (size_t)s->band_rows * wide);
-    ok = ok && !dev_alloc(s, (void **)&s->a8_scales, (size_t)s->band_rows * sizeof(float));
-    ok = ok && !dev_alloc(s, &s->qkv, (size_t)s->band_rows * n_qkv * e);
-    ok = ok && !dev_alloc(s, (void **)&s->h, (size_t)s->band_rows * d_hidden * sizeof(float));
+    ok = ok && !alloc_scratch(s, &s->scratch[0]);
     ok = ok && !dev_alloc(s, &s->host_stage, (size_t)max_rows * d_model * e);
     ok = ok && !dev_alloc(s, &s->host_out, (size_t)max_rows * d_model * e);
     ok = ok && cudaStreamCreateWithFlags(&s->own_stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -205,10 +235,15 @@ void b200_w8a8_stack_destroy(void *handle) {
         cudaFree(L.g_mlp);
     }
     for (int i = 0; i < 3; ++i) cudaFree(s->tok[i]);
-    cudaFree(s->a8);
-    cudaFree(s->a8_scales);
-    cudaFree(s->qkv);
-    cudaFree(s->h);
+    for (auto &w : s->scratch) {
+        cudaFree(w.a8);
+        cudaFree(w.a8_scales);
+        cudaFree(w.qkv);
+        cudaFree(w.h);
+    }
+    if (s->lane_stream) cudaStreamDestroy(s->lane_stream);
+    if (s->ev_fork) cudaEventDestroy(s->ev_fork);
+    if (s->ev_join) cudaEventDestroy(s->ev_join);
     cudaFree(s->host_stage);
     cudaFree(s->host_out);
     if (s->own_stream) cudaStreamDestroy(s->own_stream);
@@ -232,6 +267,24 @@ int b200_w8a8_stack_set_layer(void *handle, int layer, const float *w_qkv, const
     if (upload_vec(s, &L.g_ctrl, g_ctrl, s->d)) return 1;
     if (upload_vec(s, &L.g_mlp, g_mlp, s->d)) return 1;
     L.loaded = true;
+    return 0;
+}
+
+int b200_w8a8_stack_set_lanes(void *handle, int lanes) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s || lanes < 1 || lanes > 2) return fail("invalid stack_set_lanes (1 or 2 lanes)");
+    if (lanes == 2 && !s->lane_stream) {
+        if (alloc_scratch(s, &s->scratch[1])) return 1;
+        if (cudaStreamCreateWithFlags(&s->lane_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming) != cudaSuccess)
+            return fail("creating the second lane's stream failed");
+    }
+    if (lanes != s->lanes) {
+        for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);
+        s->graphs.clear();
+        s->lanes = lanes;
+    }
     return 0;
 }
 
