@@ -38,7 +38,7 @@ WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),
     "cfg2": (2048, 4, "bf16", 0),
-    "cfg3": (None, 1, "fp16", 4096),    # 64 worlds x 2048 rows dealt over the ranks (strong scaling)
+    "cfg3": (None, 1, "fp16", 8192),    # 64 worlds x 2048 rows dealt over the ranks (strong scaling)
 }
 CFG3_WORLDS, CFG3_ROWS_PER_WORLD = 64, 2048
 SKINNY_SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048)]  # (K, N) of config 4
@@ -161,11 +161,23 @@ def small_layer_for_cpu(ref):
     return ref.make_layer(0)
 
 
+def use_all_host_threads():
+    """torchrun pins OMP_NUM_THREADS=1; the CPU arm should use every core the box offers."""
+    import torch
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        pass
+    torch.set_num_threads(max(n, 1))
+    return torch.get_num_threads()
+
+
 def run_cpu_baseline(budget_s: float = 15.0):
     """Times a bounded sample of the headline workload on the host: rows of one layer."""
     import torch
     ref = load_oracle()
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     lw = small_layer_for_cpu(ref)
     x = ref.make_tokens(512, 0, torch.float16)
     t_probe = cpu_layer_seconds(ref, 32, lw, x)
@@ -184,7 +196,7 @@ def run_reference_arm(args):
     if rank != 0:
         return 0
     ref = load_oracle()
-    cores = torch.get_num_threads()
+    cores = use_all_host_threads()
     lw = small_layer_for_cpu(ref)
     x = ref.make_tokens(512, 0, torch.float16)
     t_probe = cpu_layer_seconds(ref, 32, lw, x)

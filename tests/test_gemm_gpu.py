@@ -180,7 +180,9 @@ def test_split_k_linear_bit_exact(pkg, ref, m, k, n, forced):
 
 def test_split_k_planner_reports_workspace(pkg):
     lib = pkg.lib()
-    assert lib.b200_w8a8_linear_workspace_size(16, 65536, 64) > 0       # one tile, very long K: the planner splits
+    # one tile, very long K that no cluster size divides (515 slabs): the split goes through the workspace
+    assert lib.b200_w8a8_linear_workspace_size(16, 515 * 128, 64) > 0
+    assert lib.b200_w8a8_linear_workspace_size(16, 65536, 64) == 0      # a cluster split needs no workspace
     assert lib.b200_w8a8_linear_workspace_size(16384, 2048, 6144) == 0  # plenty of tiles: no split
 
 

@@ -550,7 +550,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t ring = smem_u32(smem);
                 cluster_sync_all();  // every CTA of the cluster has finished reading its operand ring
                 if (warp == 2 && lane == 0) trace_mark(p, 8);
-                if (ok) {
+                if (ok && row0 < p.M) {  // a sub-partition whose 32 rows all lie beyond M has nothing to send
 #pragma unroll 1
                     for (int c = 0; c < kChunks; ++c) {
                         const int col_in_tile = half * kCols + c * 32;
@@ -576,7 +576,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (warp == 2 && lane == 0) trace_mark(p, 9);
                 cluster_sync_all();  // all partial slices have landed in their owners
                 if (warp == 2 && lane == 0) trace_mark(p, 10);
-                if (ok) {
+                if (ok && row0 < p.M) {
 #pragma unroll 1
                     for (int j = half; j < own_chunks; j += 2) {
                         const int col_in_tile = (int)rank * slice_cols + j * 32;
@@ -910,10 +910,11 @@ Plan make_plan(int m, int k, int n, int sms, bool allow_workspace) {
         const long long tiles = (long long)mb * ((n + bn - 1) / bn);
         for (int mode = 0; mode <= 2; ++mode) {
             if (mode == 1 && !(allow_workspace && (n % 4) == 0 && tiles <= 1024)) continue;
-            const int max_splits = mode == 0 ? 1 : (mode == 2 ? 4 : 8);
-            for (int sp = (mode == 0 ? 1 : 2); sp <= max_splits; sp *= (mode == 2 ? 2 : 1), sp += (mode == 2 ? 0 : 1)) {
+            const int max_splits = mode == 0 ? 1 : 8;
+            for (int sp = (mode == 0 ? 1 : 2); sp <= max_splits; ++sp) {
                 if (sp > 1 && kblocks / sp < 2) break;
-                if (mode == 2 && (bn / sp < 32 || kblocks % sp != 0)) break;
+                // a cluster split hands each CTA a whole number of 32-column chunks and of K slabs
+                if (mode == 2 && (bn % (32 * sp) != 0 || kblocks % sp != 0)) continue;
                 const long long work = tiles * sp;
                 if (sp > 1 && work > sms) break;  // keep all partials of a launch in one wave
                 const int kbps = (kblocks + sp - 1) / sp;
@@ -922,11 +923,12 @@ Plan make_plan(int m, int k, int n, int sms, bool allow_workspace) {
                 // one SM pulls ~150 KB/us through L2, but with ~100+ CTAs marching over the same
                 // A tiles a K slab has not been seen to take less than ~0.3 us (measured)
                 double t_load = (a_kb + bn * (double)BK / 1024.0) / 150.0;
-                if (work >= 64 && t_load < 0.30) t_load = 0.30;
+                if (t_load < 0.30) t_load = 0.30;
                 const double t_epi = 0.45 * bn / 64.0 / (mode == 2 ? sp : 1);
                 // cluster exchange: (sp-1)/sp of a 128 x bn int32 tile per CTA at ~20 KB/us (measured)
+                const int live_quarters = m >= BM ? 4 : (m + 31) / 32;  // 32-row groups that hold real rows
                 const double t_red = mode == 1 ? 3.0 + 1.0 * sp * bn / 64.0
-                                               : (mode == 2 ? 1.0 + (sp - 1.0) / sp * bn * 0.0256 : 0.0);
+                                               : (mode == 2 ? 1.0 + (sp - 1.0) / sp * bn * 0.0256 * live_quarters / 4.0 : 0.0);
                 const double t = waves * (0.3 + kbps * (t_mma > t_load ? t_mma : t_load) + t_epi + t_red);
                 if (t < best_t) {
                     best_t = t;
@@ -996,7 +998,7 @@ int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_byte
     }
     if (pl.mode == 2) {
         const int kblocks = (a.k + BK - 1) / BK;
-        if (pl.bn / pl.splits < 32 || kblocks % pl.splits != 0 || pl.splits > 8)
+        if (pl.bn % (32 * pl.splits) != 0 || kblocks % pl.splits != 0 || pl.splits > 8)
             return fail("cluster split-K needs BN/splits >= 32 and K blocks divisible by splits (bn=%d splits=%d)",
                         pl.bn, pl.splits);
     }
