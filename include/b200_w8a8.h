@@ -110,6 +110,10 @@ int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, 
  * the reference, whose tile shape is a compile-time template argument
  * (src/world_cuda_ops.cu:529-548). */
 void b200_w8a8_set_tile_width(int bn);
+/* Tuning aid: 0 = the planner decides when two CTAs share one 256 x 256 tile (cta_group::2 MMA),
+ * 1 = whenever the launch allows it (M > 128, unsplit 256-wide tiles, aligned buffers,
+ * N % 32 == 0), 2 = never.  No counterpart in the reference. */
+void b200_w8a8_set_pair_mma(int mode);
 /* Switches programmatic dependent launch on (default) or off for every later launch of the
  * process.  When on, a kernel of this library may be scheduled while its predecessor in the
  * stream is still finishing, and waits on the device before it touches dependent data; off

@@ -210,3 +210,30 @@ def test_cluster_split_k_linear_bit_exact(pkg, ref, m, k, n, bn, splits, out_dty
         assert torch.equal(acc.cpu(), ref.gemm_i8_i32(a, b))
     finally:
         pkg.lib().b200_w8a8_set_tile_width(0)
+
+
+@pytest.fixture
+def pair_mma(pkg):
+    pkg.lib().b200_w8a8_set_pair_mma(1)  # two CTAs per 256 x 256 tile wherever the launch allows it
+    yield
+    pkg.lib().b200_w8a8_set_pair_mma(0)
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 128, 256), (512, 2048, 6144), (130, 256, 512), (300, 4096, 544),
+                                   (2048, 2048, 2048), (4224, 256, 384), (1024, 8192, 2048)])
+def test_pair_mma_gemm_bit_exact(pkg, ref, pair_mma, m, k, n):
+    """cta_group::2: a cluster of two CTAs shares one tile (each loads half of the W rows)."""
+    a, b = codes(m, k, m + 3), codes(n, k, n + 5)
+    acc = pkg.gemm_i8_i32(a.to(DEV), b.to(DEV))
+    assert pkg.poll_status() == 0
+    assert torch.equal(acc.cpu(), ref.gemm_i8_i32(a, b))
+    g = torch.Generator().manual_seed(m)
+    sx = torch.rand(m, generator=g) * 0.05 + 0.01
+    sw = torch.rand(n, generator=g) * 2e-4 + 1e-5
+    bias = torch.randn(n, generator=g) * 0.1
+    res = torch.randn(m, n, generator=g).half()
+    want = ref.linear_w8a8(a, sx, b, sw, bias=bias, residual=res, out_dtype=torch.float16)
+    got = pkg.linear(a.to(DEV), sx.to(DEV), slab(b).to(DEV), sw.to(DEV), n=n, w_layout=pkg.W_SLAB128,
+                     bias=bias.to(DEV), residual=res.to(DEV), out_dtype=torch.float16)
+    assert pkg.poll_status() == 0
+    assert torch.equal(got.cpu(), want)

@@ -44,6 +44,7 @@ _PROTOTYPES = {
     "b200_w8a8_gemm_i8_i32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_set_tile_width": (None, [c_int]),
     "b200_w8a8_set_trace_buffer": (None, [c_void_p]),
+    "b200_w8a8_set_pair_mma": (None, [c_int]),
     "b200_w8a8_set_overlapped_launch": (None, [c_int]),
     "b200_w8a8_linear_workspace_size": (c_size_t, [c_int, c_int, c_int]),
     "b200_w8a8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

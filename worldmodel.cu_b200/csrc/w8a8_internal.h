@@ -105,6 +105,7 @@ int gemm_poll_status(int *status_out);
 int linear_static_scratch(const LinearArgs &a, cudaStream_t stream);
 size_t static_scratch_capacity();
 void gemm_set_tile_width(int bn);
+void gemm_set_pair_mode(int mode);
 void gemm_set_trace_buffer(unsigned long long *dev_buf);
 
 // ---- pack_weights.cpp
