@@ -170,6 +170,26 @@ int b200_w8a8_linear_static_scratch(const int8_t *x_i8, const float *x_scales, c
                                     const void *residual, int64_t ldr, void *y, int y_dtype, int64_t ldy, int m,
                                     int k, int n, int act, void *stream);
 
+/* cos / sin of every (token, rotary pair) for the positions of one frame: [tokens, d_head/2]
+ * fp32 each, the values wm_cuda_qkv_fused_rms_rope_i32_dequant derives per head from the
+ * frequency tables of wm_cuda_fill_rope_tables (src/world_cuda.cu:561-577).  Positions are
+ * the same for every layer, so one call serves a whole pass. */
+int b200_w8a8_rope_tables(const int64_t *x_pos, const int64_t *y_pos, const int64_t *t_pos, const float *xy,
+                          const float *inv_t, int tokens, int d_head, int width, int height, float *cos_out,
+                          float *sin_out, void *stream);
+
+/* The QKV linear with its consumer as the epilogue: int8 GEMM over
+ * N = (n_heads + 2 n_kv_heads) * d_head columns, dequantized (+ bias, nullable), per-head
+ * RMSNorm + rotary embedding on Q and K, written head-major fp32 q[Hq,T,d], k[Hkv,T,d],
+ * v[Hkv,T,d] -- the pair wm_cuda_gemm_i8_i32 + wm_cuda_qkv_fused_rms_rope_i32_dequant
+ * (src/world_cuda.cu:1840-1880; src/world_cuda_ops.cu:1229-1305) without the int32 round
+ * trip, bit-identical to that pair.  d_head must be 64 (a head is two 32-column accumulator
+ * loads of one thread); other head sizes use the two-call form. */
+int b200_w8a8_linear_qkv_heads(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                               const float *w_scales, const float *bias, const float *rope_cos,
+                               const float *rope_sin, float *q, float *k, float *v, int tokens, int k_dim,
+                               int n_heads, int n_kv_heads, int d_head, float eps, void *stream);
+
 /* ---- weights (HOST pointers) ------------------------------------------------------ */
 
 /* Per-output-channel symmetric int8 quantization of host fp32 w[N,K] into `layout`,
@@ -223,6 +243,29 @@ int b200_w8a8_stack_set_act_dtype(void *stack, int act_dtype);
 size_t b200_w8a8_stack_device_bytes(void *stack);
 /* Kernels enqueued (or replayed) by the most recent forward. */
 long long b200_w8a8_stack_launches_per_forward(void *stack);
+
+/* ---- offline packed-weight file (HOST side; the writer needs no GPU) ---------------- */
+
+/* Writes the int8 codes (slab layout) and per-channel scales of every layer, plus the three
+ * norm vectors, to one file so that start-up copies bytes instead of re-quantizing fp32
+ * weights.  The reference quantizes on every start (copy_f32_to_i8_per_output_device,
+ * src/world_cuda.cu:153-222) and names this export as the next step of its roadmap
+ * (docs/cuda_w8a8_optimization.md:357).  File: 64-byte header {magic "B2W8A8WF", version,
+ * layout, d, n_qkv, hidden, layers, payload bytes, FNV-1a 64 of the payload}, then per layer
+ * qkv/out/ctrl/up/down as codes + fp32 scales and g_attn/g_ctrl/g_mlp as fp32.
+ * create -> add_layer x n_layers (host fp32 pointers, as stack_set_layer) -> close. */
+void *b200_w8a8_weight_file_create(const char *path, int d_model, int n_qkv, int d_hidden, int n_layers);
+int b200_w8a8_weight_file_add_layer(void *writer, const float *w_qkv, const float *w_out, const float *w_ctrl,
+                                    const float *w_up, const float *w_down, const float *g_attn,
+                                    const float *g_ctrl, const float *g_mlp, int threads);
+int b200_w8a8_weight_file_close(void *writer);
+/* Validates the header (and with verify != 0 the payload checksum); out-params nullable. */
+int b200_w8a8_weight_file_info(const char *path, int *d_model, int *n_qkv, int *d_hidden, int *n_layers,
+                               int verify);
+/* Loads every layer of a stack from such a file (dimensions must match the stack's; the
+ * checksum is verified first), or writes the stack's resident weights to one. */
+int b200_w8a8_stack_load_weights(void *stack, const char *path);
+int b200_w8a8_stack_save_weights(void *stack, const char *path);
 
 #ifdef __cplusplus
 }

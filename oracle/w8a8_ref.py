@@ -192,11 +192,14 @@ def rope_phase(pair_id, x_pos, y_pos, t_pos, xy, inv_t, width, height, d_xy):
 
 
 def qkv_fused_rms_rope_i32_dequant(acc, row_scales, w_scales, x_pos, y_pos, t_pos, xy, inv_t,
-                                   n_heads, n_kv_heads, d_head, width, height, eps):
-    """src/world_cuda_ops.cu:1229-1305.  Returns head-major fp32 q[Hq,T,d], k, v[Hkv,T,d]."""
+                                   n_heads, n_kv_heads, d_head, width, height, eps, bias=None):
+    """src/world_cuda_ops.cu:1229-1305.  Returns head-major fp32 q[Hq,T,d], k, v[Hkv,T,d].
+    `bias` (not in the reference, whose QKV linear has none) is added right after the dequantization."""
     T = acc.shape[0]
     q_dim, kv_dim = n_heads * d_head, n_kv_heads * d_head
     z = dequant(acc, row_scales, w_scales)
+    if bias is not None:
+        z = z + bias.to(torch.float32)[None, :]
     half, d_xy = d_head // 2, d_head // 8
     phases = torch.stack([rope_phase(p, x_pos, y_pos, t_pos, xy, inv_t, width, height, d_xy)
                           for p in range(half)], dim=1).to(torch.float32)  # [T, half]

@@ -151,3 +151,29 @@ def test_stack_full_size_layers_properties(pkg, ref):
     got = pkg.linear(q1g, s1g, packed.to(DEV), swp.to(DEV), w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
     assert same(q1g, q1) and same(got, want)
     stack.close()
+
+
+def test_stack_loaded_from_a_packed_weight_file_equals_the_quantizing_loader(pkg, ref, tmp_path):
+    """The offline file (written on the host without a GPU) and set_layer give the same device
+    weights: identical forward output, and saving the resident weights reproduces the file."""
+    n_layers, rows = 2, 160
+    layers = [ref.make_layer_fp32(l, D, NQKV, HID) for l in range(n_layers)]
+    path = tmp_path / "stack.w8a8"
+    pkg.write_weight_file(path, D, NQKV, HID, layers, threads=4)
+    a = pkg.LinearStack(D, NQKV, HID, n_layers, max_rows=rows)
+    for l, (ws, gs) in enumerate(layers):
+        a.set_layer(l, ws, gs, threads=4)
+    b = pkg.LinearStack(D, NQKV, HID, n_layers, max_rows=rows)
+    with pytest.raises(pkg.W8A8Error, match="before every layer was loaded"):
+        b.forward(torch.zeros(rows, D, dtype=torch.float16, device=DEV))
+    b.load_weights(path)
+    x = ref.make_tokens(rows, 4, torch.float16, D).to(DEV)
+    assert same(a.forward(x), b.forward(x))
+    saved = tmp_path / "saved.w8a8"
+    a.save_weights(saved)
+    assert saved.read_bytes() == path.read_bytes()
+    wrong = pkg.LinearStack(D, NQKV, HID, n_layers + 1, max_rows=rows)
+    with pytest.raises(pkg.W8A8Error, match="the stack is"):
+        wrong.load_weights(path)
+    for s in (a, b, wrong):
+        s.close()

@@ -40,6 +40,8 @@ _PROTOTYPES = {
     "b200_w8a8_dequant_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                            c_int, c_int, c_void_p]),
     "b200_w8a8_qkv_rms_rope_dequant": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_float, c_void_p]),
+    "b200_w8a8_rope_tables": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p] * 3),
+    "b200_w8a8_linear_qkv_heads": (c_int, [c_void_p] * 3 + [c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_void_p]),
     "b200_w8a8_gemm_i8_i32_can_implement": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int]),
     "b200_w8a8_gemm_i8_i32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_set_tile_width": (None, [c_int]),
@@ -66,6 +68,12 @@ _PROTOTYPES = {
     "b200_w8a8_stack_set_lanes": (c_int, [c_void_p, c_int]),
     "b200_w8a8_stack_device_bytes": (c_size_t, [c_void_p]),
     "b200_w8a8_stack_launches_per_forward": (ctypes.c_longlong, [c_void_p]),
+    "b200_w8a8_weight_file_create": (c_void_p, [ctypes.c_char_p, c_int, c_int, c_int, c_int]),
+    "b200_w8a8_weight_file_add_layer": (c_int, [c_void_p] + [c_void_p] * 8 + [c_int]),
+    "b200_w8a8_weight_file_close": (c_int, [c_void_p]),
+    "b200_w8a8_weight_file_info": (c_int, [ctypes.c_char_p] + [ctypes.POINTER(c_int)] * 4 + [c_int]),
+    "b200_w8a8_stack_load_weights": (c_int, [c_void_p, ctypes.c_char_p]),
+    "b200_w8a8_stack_save_weights": (c_int, [c_void_p, ctypes.c_char_p]),
 }
 
 _lib = None
@@ -178,6 +186,31 @@ def qkv_rms_rope_dequant(acc, row_scales, w_scales, x_pos, y_pos, t_pos, xy, inv
     return q, k, v
 
 
+def rope_tables(x_pos, y_pos, t_pos, xy, inv_t, d_head, width, height):
+    """cos / sin tables [T, d_head/2] of one frame's positions (see b200_w8a8_rope_tables)."""
+    import torch
+    T = x_pos.shape[0]
+    c = torch.empty(T, d_head // 2, dtype=torch.float32, device=x_pos.device)
+    s = torch.empty_like(c)
+    _check(lib().b200_w8a8_rope_tables(_ptr(x_pos), _ptr(y_pos), _ptr(t_pos), _ptr(xy), _ptr(inv_t), T, d_head, width,
+                                       height, _ptr(c), _ptr(s), _stream()), "rope_tables")
+    return c, s
+
+
+def linear_qkv_heads(x_i8, x_scales, w_i8, w_scales, rope_cos, rope_sin, n_heads, n_kv_heads, d_head, eps,
+                     bias=None, w_layout=W_ROW_MAJOR):
+    """QKV linear + per-head RMSNorm + rotary embedding in one kernel; returns head-major fp32 q, k, v."""
+    import torch
+    T, kdim = x_i8.shape
+    q = torch.empty(n_heads, T, d_head, dtype=torch.float32, device=x_i8.device)
+    k = torch.empty(n_kv_heads, T, d_head, dtype=torch.float32, device=x_i8.device)
+    v = torch.empty(n_kv_heads, T, d_head, dtype=torch.float32, device=x_i8.device)
+    _check(lib().b200_w8a8_linear_qkv_heads(_ptr(x_i8), _ptr(x_scales), _ptr(w_i8), w_layout, _ptr(w_scales), _ptr(bias),
+                                            _ptr(rope_cos), _ptr(rope_sin), _ptr(q), _ptr(k), _ptr(v), T, kdim, n_heads,
+                                            n_kv_heads, d_head, eps, _stream()), "linear_qkv_heads")
+    return q, k, v
+
+
 def gemm_i8_i32(x_i8, w_i8, n=None, w_layout=W_ROW_MAJOR):
     import torch
     m, k = x_i8.shape
@@ -240,6 +273,36 @@ def pack_weight(w_f32_cpu, layout=W_SLAB128, threads=0):
     return packed, scales
 
 
+def write_weight_file(path, d_model, n_qkv, d_hidden, layers, threads=0):
+    """Quantizes and packs `layers` (an iterable of (five fp32 CPU weights, three fp32 norm vectors),
+    as LinearStack.set_layer takes them) into one packed-weight file.  Host only: needs no GPU."""
+    layers = list(layers)
+    w = lib().b200_w8a8_weight_file_create(str(path).encode(), d_model, n_qkv, d_hidden, len(layers))
+    if not w:
+        raise W8A8Error("weight_file_create failed: " + lib().b200_w8a8_last_error().decode())
+    rc, msg = 0, ""
+    for weights_fp32, gammas in layers:
+        ws = [t.contiguous().float() for t in weights_fp32]
+        gs = [t.contiguous().float() for t in gammas]
+        rc = lib().b200_w8a8_weight_file_add_layer(w, *[t.data_ptr() for t in ws], *[t.data_ptr() for t in gs],
+                                                   threads)
+        if rc:
+            msg = lib().b200_w8a8_last_error().decode()
+            break
+    rc_close = lib().b200_w8a8_weight_file_close(w)
+    if rc:
+        raise W8A8Error("weight_file_add_layer failed: " + msg)
+    _check(rc_close, "weight_file_close")
+
+
+def weight_file_info(path, verify=True):
+    """Returns (d_model, n_qkv, d_hidden, n_layers) of a packed-weight file; raises if it is invalid."""
+    vals = [c_int(0) for _ in range(4)]
+    _check(lib().b200_w8a8_weight_file_info(str(path).encode(), *[ctypes.byref(v) for v in vals], int(verify)),
+           "weight_file_info")
+    return tuple(v.value for v in vals)
+
+
 class LinearStack:
     """Thin holder of a b200_w8a8_stack handle (see include/b200_w8a8.h)."""
 
@@ -273,6 +336,13 @@ class LinearStack:
         _check(lib().b200_w8a8_stack_forward_host(self.handle, x_host.data_ptr(), y_host.data_ptr(), x_host.shape[0],
                                                   steps, int(use_graph)), "stack_forward_host")
         return y_host
+
+    def load_weights(self, path):
+        """Loads every layer from a packed-weight file (see write_weight_file)."""
+        _check(lib().b200_w8a8_stack_load_weights(self.handle, str(path).encode()), "stack_load_weights")
+
+    def save_weights(self, path):
+        _check(lib().b200_w8a8_stack_save_weights(self.handle, str(path).encode()), "stack_save_weights")
 
     def set_lanes(self, lanes):
         _check(lib().b200_w8a8_stack_set_lanes(self.handle, lanes), "stack_set_lanes")

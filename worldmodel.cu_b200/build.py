@@ -23,6 +23,7 @@ SOURCES = [
     "dequant_ops.cu",
     "gemm_i8_tcgen05.cu",
     "pack_weights.cpp",
+    "weight_file.cpp",
     "dropin.cu",
     "linear_stack.cu",
 ]

@@ -82,6 +82,25 @@ int b200_w8a8_qkv_rms_rope_dequant(const int32_t *qkv_acc, const float *row_scal
                                 n_heads, n_kv_heads, d_head, width, height, eps, as_stream(stream));
 }
 
+int b200_w8a8_rope_tables(const int64_t *x_pos, const int64_t *y_pos, const int64_t *t_pos, const float *xy,
+                          const float *inv_t, int tokens, int d_head, int width, int height, float *cos_out,
+                          float *sin_out, void *stream) {
+    return rope_tables(x_pos, y_pos, t_pos, xy, inv_t, tokens, d_head, width, height, cos_out, sin_out,
+                       as_stream(stream));
+}
+
+int b200_w8a8_linear_qkv_heads(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                               const float *w_scales, const float *bias, const float *rope_cos,
+                               const float *rope_sin, float *q, float *k, float *v, int tokens, int k_dim,
+                               int n_heads, int n_kv_heads, int d_head, float eps, void *stream) {
+    QkvHeadsArgs a{};
+    a.x = x_i8; a.row_scales = x_scales; a.w = w_i8; a.w_layout = w_layout; a.col_scales = w_scales; a.bias = bias;
+    a.rope_cos = rope_cos; a.rope_sin = rope_sin; a.q = q; a.k = k; a.v = v;
+    a.tokens = tokens; a.k_dim = k_dim; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.d_head = d_head;
+    a.eps = eps;
+    return linear_qkv_heads(a, as_stream(stream));
+}
+
 static LinearArgs raw_gemm_args(const int8_t *x, const int8_t *w, int w_layout, const int32_t *acc, int m, int k,
                                 int n) {
     LinearArgs a{};

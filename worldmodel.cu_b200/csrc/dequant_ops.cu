@@ -213,7 +213,37 @@ __global__ void __launch_bounds__(256) qkv_rms_rope_dequant_kernel(
     }
 }
 
+// cos / sin of every (token, rotary pair): the values the QKV consumer would compute per head,
+// computed once per frame (positions do not change from layer to layer).
+__global__ void __launch_bounds__(256) rope_tables_kernel(const int64_t *__restrict__ x_pos,
+                                                          const int64_t *__restrict__ y_pos,
+                                                          const int64_t *__restrict__ t_pos,
+                                                          const float *__restrict__ xy, const float *__restrict__ inv_t,
+                                                          int T, int half, int d_xy, int width, int height,
+                                                          float *__restrict__ cos_out, float *__restrict__ sin_out) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)T * half) return;
+    const int t = (int)(i / half), pair = (int)(i - (long long)t * half);
+    const float phase = rope_phase(pair, x_pos[t], y_pos[t], t_pos[t], xy, inv_t, width, height, d_xy);
+    cos_out[i] = cosf(phase);
+    sin_out[i] = sinf(phase);
+}
+
 }  // namespace
+
+int rope_tables(const int64_t *x_pos, const int64_t *y_pos, const int64_t *t_pos, const float *xy, const float *inv_t,
+                int tokens, int d_head, int width, int height, float *cos_out, float *sin_out, cudaStream_t stream) {
+    if (!x_pos || !y_pos || !t_pos || !xy || !inv_t || !cos_out || !sin_out || tokens < 0 || d_head <= 0 ||
+        width <= 0 || height <= 0 || d_head % 8 != 0)
+        return fail("invalid rope_tables arguments tokens=%d d_head=%d", tokens, d_head);
+    if (tokens == 0) return 0;
+    const long long n = (long long)tokens * (d_head / 2);
+    launch_kernel(rope_tables_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x_pos, y_pos, t_pos, xy,
+                  inv_t, tokens, d_head / 2, d_head / 8, width, height, cos_out, sin_out);
+    return check_launch("rope_tables");
+}
 
 int dequant_residual(const int32_t *acc, const float *row_scales, const float *col_scales, const void *residual,
                      int res_dtype, const float *gate, void *out, int out_dtype, int rows, int cols,

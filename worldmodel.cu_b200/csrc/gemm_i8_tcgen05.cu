@@ -54,15 +54,20 @@ constexpr int kSmemBudget = 192 * 1024;          // operand pipeline
 constexpr int kStagingPerWarp = 4096;            // epilogue staging block per warp
 constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
 
-template <int BN>
+// WIDE: the QKV-heads epilogue transposes its table reads and its output through shared
+// memory and needs 8 KB per epilogue warp; the operand ring gives up 32 KB for it.
+template <int BN, bool WIDE = false>
 struct Cfg {
     static constexpr int kABytes = BM * BK;
     static constexpr int kBBytes = BN * BK;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = kSmemBudget / kStageBytes > 10 ? 10 : kSmemBudget / kStageBytes;
+    static constexpr int kWarpStaging = WIDE ? 2 * kStagingPerWarp : kStagingPerWarp;
+    static constexpr int kStagingTotal = kEpilogueWarps * kWarpStaging;
+    static constexpr int kRing = kSmemBudget - (kStagingTotal - kStagingBytes);
+    static constexpr int kStages = kRing / kStageBytes > 10 ? 10 : kRing / kStageBytes;
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
     static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingTotal + kBarBytes + 1024;  // + alignment slack
 };
 
 struct GemmParams {
@@ -89,7 +94,17 @@ struct GemmParams {
     int tma_store;  // the output can be written through the TMA store path
     int static_weights;  // W may be fetched before the predecessor kernel has completed
     unsigned long long *trace;  // tuning aid: per-CTA timestamps (8 per CTA), or null
+    // QKV consumer epilogue (OUT == kOutQkvHeads only): head-major fp32 outputs and rotary tables
+    float *q_heads, *k_heads, *v_heads;  // [Hq,M,64], [Hkv,M,64], [Hkv,M,64]
+    const float *rope_cos, *rope_sin;    // [M,32]
+    int n_heads, n_kv_heads;
+    float head_eps;
 };
+
+// Pseudo output type of the QKV consumer epilogue: per-head RMSNorm + rotary embedding of Q
+// and K, plain dequantization of V, all written head-major in fp32.
+constexpr int kOutQkvHeads = 4;
+constexpr int kHeadDim = 64;
 
 __device__ __forceinline__ void trace_mark(const GemmParams &p, int slot) {
     if (p.trace) p.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
@@ -361,17 +376,136 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const CUtens
     else if (row_live) store32_direct<OUT>(p, w, row, col0);
 }
 
+// QKV consumer as a GEMM epilogue: one thread holds one token's 64 accumulators of one head
+// (two 32-column TMEM loads), so the per-head sum of squares needs no shuffle.  Q and K heads
+// are normalised by 1/sqrt(mean(z^2) + eps) (fp64 sum) and rotated with the token's cos/sin
+// row: out[p] = a*c - b*s, out[32+p] = b*c + a*s for the interleaved pair (a, b) =
+// (z[2p], z[2p+1]); V heads are only dequantized.
+//
+// A row per thread is the worst global access pattern (32 lines per instruction), so both
+// directions go through shared memory with a 16-byte XOR swizzle that is conflict-free for
+// the row-per-thread side and for the coalesced side:
+//   tables  [32 rows][8 x 16 B] of cos and of sin, loaded coalesced once per tile by the two
+//           warps that share the 32 rows (one loads cos, the other sin);
+//   output  a head's 32 rows x 256 B are contiguous in the head-major result; they leave in
+//           two passes of 32 rows x 128 B, written row-per-thread, read back 4 rows per
+//           instruction and stored as full 128-byte lines.
+__device__ __forceinline__ uint32_t swz16(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+__device__ __forceinline__ void qkv_store_pass(uint8_t *out_stage, float *head_base, int row0, int lane, int M,
+                                               int byte_off) {
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + (lane >> 3), c = lane & 7;
+        const float4 val = *reinterpret_cast<const float4 *>(out_stage + swz16(r, c));
+        if (row0 + r < M)
+            *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(head_base + (long long)(row0 + r) * kHeadDim) +
+                                        byte_off + c * 16) = val;
+    }
+    __syncwarp();  // the block is free again
+}
+
+__device__ __forceinline__ void qkv_head_epilogue(const GemmParams &p, uint32_t taddr, const uint8_t *cos_tab,
+                                                  const uint8_t *sin_tab, uint8_t *out_stage, int row0, int lane,
+                                                  int head, float row_scale) {
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32(taddr, ra);
+    tmem_ld_32x32(taddr + 32u, rb);
+    tmem_ld_wait();
+    const int col0 = head * kHeadDim;
+    float z[kHeadDim];
+    {
+        const float4 *cs4 = reinterpret_cast<const float4 *>(p.col_scales + col0);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float4 ca = __ldg(cs4 + g), cb = __ldg(cs4 + 8 + g);
+            z[4 * g + 0] = dequant_acc((int)ra[4 * g + 0], row_scale, ca.x);
+            z[4 * g + 1] = dequant_acc((int)ra[4 * g + 1], row_scale, ca.y);
+            z[4 * g + 2] = dequant_acc((int)ra[4 * g + 2], row_scale, ca.z);
+            z[4 * g + 3] = dequant_acc((int)ra[4 * g + 3], row_scale, ca.w);
+            z[32 + 4 * g + 0] = dequant_acc((int)rb[4 * g + 0], row_scale, cb.x);
+            z[32 + 4 * g + 1] = dequant_acc((int)rb[4 * g + 1], row_scale, cb.y);
+            z[32 + 4 * g + 2] = dequant_acc((int)rb[4 * g + 2], row_scale, cb.z);
+            z[32 + 4 * g + 3] = dequant_acc((int)rb[4 * g + 3], row_scale, cb.w);
+        }
+    }
+    if (p.bias) {
+        const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + col0);
+#pragma unroll
+        for (int g = 0; g < 16; ++g) {
+            const float4 b = __ldg(b4 + g);
+            z[4 * g + 0] = __fadd_rn(z[4 * g + 0], b.x);
+            z[4 * g + 1] = __fadd_rn(z[4 * g + 1], b.y);
+            z[4 * g + 2] = __fadd_rn(z[4 * g + 2], b.z);
+            z[4 * g + 3] = __fadd_rn(z[4 * g + 3], b.w);
+        }
+    }
+    const int qk_heads = p.n_heads + p.n_kv_heads;
+    if (head >= qk_heads) {  // V: dequantized only (warp-uniform branch)
+        float *base = p.v_heads + (long long)(head - qk_heads) * p.M * kHeadDim;
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+                *reinterpret_cast<float4 *>(out_stage + swz16(lane, g)) =
+                    make_float4(z[32 * pass + 4 * g], z[32 * pass + 4 * g + 1], z[32 * pass + 4 * g + 2],
+                                z[32 * pass + 4 * g + 3]);
+            qkv_store_pass(out_stage, base, row0, lane, p.M, pass * 128);
+        }
+        return;
+    }
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;  // four chains: fp64 latency, not order, is the concern
+#pragma unroll
+    for (int j = 0; j < kHeadDim; j += 4) {
+        s0 = fma((double)z[j], (double)z[j], s0);
+        s1 = fma((double)z[j + 1], (double)z[j + 1], s1);
+        s2 = fma((double)z[j + 2], (double)z[j + 2], s2);
+        s3 = fma((double)z[j + 3], (double)z[j + 3], s3);
+    }
+    const double ss = (s0 + s1) + (s2 + s3);
+    const float inv = (float)(1.0 / sqrt(ss / (double)kHeadDim + (double)p.head_eps));
+    float *base = head < p.n_heads ? p.q_heads + (long long)head * p.M * kHeadDim
+                                   : p.k_heads + (long long)(head - p.n_heads) * p.M * kHeadDim;
+    // pass 0: out[0..31] = a*c - b*s; pass 1: out[32..63] = b*c + a*s
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const float4 c = *reinterpret_cast<const float4 *>(cos_tab + swz16(lane, g));
+        const float4 sn = *reinterpret_cast<const float4 *>(sin_tab + swz16(lane, g));
+        const float a0 = __fmul_rn(z[8 * g + 0], inv), b0 = __fmul_rn(z[8 * g + 1], inv);
+        const float a1 = __fmul_rn(z[8 * g + 2], inv), b1 = __fmul_rn(z[8 * g + 3], inv);
+        const float a2 = __fmul_rn(z[8 * g + 4], inv), b2 = __fmul_rn(z[8 * g + 5], inv);
+        const float a3 = __fmul_rn(z[8 * g + 6], inv), b3 = __fmul_rn(z[8 * g + 7], inv);
+        *reinterpret_cast<float4 *>(out_stage + swz16(lane, g)) =
+            make_float4(__fsub_rn(__fmul_rn(a0, c.x), __fmul_rn(b0, sn.x)),
+                        __fsub_rn(__fmul_rn(a1, c.y), __fmul_rn(b1, sn.y)),
+                        __fsub_rn(__fmul_rn(a2, c.z), __fmul_rn(b2, sn.z)),
+                        __fsub_rn(__fmul_rn(a3, c.w), __fmul_rn(b3, sn.w)));
+        // the second half is kept in z (its inputs are consumed) until the first pass has left
+        z[8 * g + 0] = __fadd_rn(__fmul_rn(b0, c.x), __fmul_rn(a0, sn.x));
+        z[8 * g + 1] = __fadd_rn(__fmul_rn(b1, c.y), __fmul_rn(a1, sn.y));
+        z[8 * g + 2] = __fadd_rn(__fmul_rn(b2, c.z), __fmul_rn(a2, sn.z));
+        z[8 * g + 3] = __fadd_rn(__fmul_rn(b3, c.w), __fmul_rn(a3, sn.w));
+    }
+    qkv_store_pass(out_stage, base, row0, lane, p.M, 0);
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+        *reinterpret_cast<float4 *>(out_stage + swz16(lane, g)) =
+            make_float4(z[8 * g + 0], z[8 * g + 1], z[8 * g + 2], z[8 * g + 3]);
+    qkv_store_pass(out_stage, base, row0, lane, p.M, 128);
+}
+
 // SPLITK: 0 = one CTA owns the whole K range of a tile; 1 = K split over CTAs that meet in a
 // global workspace; 2 = K split over the CTAs of a cluster that meet in shared memory.
 template <int BN, int OUT, bool GENERAL, int SPLITK>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_i8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                    const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, OUT == kOutQkvHeads>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *staging = smem + C::kStages * C::kStageBytes;  // 1024-byte aligned: stage sizes are multiples of 1 KB
-    uint64_t *bar_full = reinterpret_cast<uint64_t *>(staging + kStagingBytes);
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(staging + C::kStagingTotal);
     uint64_t *bar_empty = bar_full + C::kStages;
     uint64_t *bar_tfull = bar_empty + C::kStages;
     uint64_t *bar_tempty = bar_tfull + 2;
@@ -505,7 +639,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int half = ew >> 2;          // which half of the tile's columns
         constexpr int kCols = BN / 2;      // columns per warp
         constexpr int kChunks = kCols / 32;
-        uint8_t *stage = staging + ew * kStagingPerWarp;
+        uint8_t *stage = staging + ew * C::kWarpStaging;
         pdl_wait();  // before the first read of the scales / residual and the first write of the output
         int t = 0;
         int seq = 0;  // running count of this warp's staged stores: alternates the 16-bit staging halves
@@ -530,10 +664,23 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 if (row0 + lane < p.M) row_scale = __ldg(p.row_scales + row0 + lane);
                 fetch_residual16<OUT>(p, row0 + lane, colbase, res_a);
+                if (OUT == kOutQkvHeads) {  // this warp's rotary table (cos or sin) of the 32 rows, coalesced
+                    const float *tab = half ? p.rope_sin : p.rope_cos;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = 4 * i + (lane >> 3), c = lane & 7;
+                        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (row0 + r < p.M)
+                            val = __ldg(reinterpret_cast<const float4 *>(tab + (long long)(row0 + r) * (kHeadDim / 2)) + c);
+                        *reinterpret_cast<float4 *>(stage + swz16(r, c)) = val;
+                    }
+                }
             }
             ok = mbar_wait_bounded(&bar_tfull[b], tph, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok && SPLITK != 2) break;  // (in a cluster every thread still has to meet the cluster barriers)
+            // (in a cluster every thread still has to meet the cluster barriers; the QKV-heads
+            // epilogue first lets the two warps that share a table agree on the outcome)
+            if (!ok && SPLITK != 2 && OUT != kOutQkvHeads) break;
             if (warp == 2 && lane == 0) trace_mark(p, 4);
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * BN + half * kCols);
@@ -667,6 +814,37 @@ __global__ void __launch_bounds__(kThreads, 1)
                         epilogue_chunk<OUT, true>(p, &tm_out, stage, r, res, lane, row0, col0, row_scale, seq++);
                     }
                 }
+                if (warp == 2 && lane == 0) trace_mark(p, 5);
+                continue;
+            }
+            if constexpr (OUT == kOutQkvHeads) {
+                // The two warps of a sub-partition share the 32 rows: the first 4 KB of the lower
+                // warp's staging holds the cos rows, of the upper warp's the sin rows; each warp's
+                // second 4 KB is its own output block.  (The tables were loaded before the wait.)
+                const uint8_t *cos_tab = staging + (ew & 3) * C::kWarpStaging;  // warps ew and ew + 4 share `sub`
+                const uint8_t *sin_tab = staging + (4 + (ew & 3)) * C::kWarpStaging;
+                {  // both tables are in place, and both warps saw the accumulator arrive (or neither goes on)
+                    uint32_t both;
+                    asm volatile(
+                        "{\n.reg .pred pin, pout;\nsetp.ne.u32 pin, %2, 0;\n"
+                        "barrier.cta.red.and.pred pout, %1, 64, pin;\nselp.u32 %0, 1, 0, pout;\n}"
+                        : "=r"(both)
+                        : "r"(2 + sub), "r"((uint32_t)ok)
+                        : "memory");
+                    ok = both != 0;
+                    if (!ok) break;
+                }
+#pragma unroll 1
+                for (int hh = 0; hh < kCols / kHeadDim; ++hh) {
+                    const int col0 = colbase + hh * kHeadDim;
+                    if (col0 >= p.N) break;  // warp-uniform: N is a whole number of heads
+                    qkv_head_epilogue(p, taddr + (uint32_t)(hh * kHeadDim), cos_tab, sin_tab, stage + kStagingPerWarp,
+                                      row0, lane, col0 / kHeadDim, row_scale);
+                }
+                asm volatile("bar.sync %0, 64;" ::"r"(2 + sub) : "memory");  // both warps are done with the tables
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_tempty[b]);
                 if (warp == 2 && lane == 0) trace_mark(p, 5);
                 continue;
             }
@@ -979,7 +1157,7 @@ int make_out_map(CUtensorMap *map, const void *base, int dtype, uint64_t cols, u
 
 struct DeviceInfo {
     int sms = 0;
-    bool attr_set[3][4][4] = {};
+    bool attr_set[3][5][4] = {};
     bool pair_attr_set[4] = {};
 };
 DeviceInfo &device_info(int dev) {
@@ -993,7 +1171,7 @@ DeviceInfo &device_info(int dev) {
 
 template <int BN, int OUT, bool GENERAL, int SPLITK>
 int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, OUT == kOutQkvHeads>;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     DeviceInfo &di = device_info(dev);
@@ -1293,6 +1471,47 @@ int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_byte
 #undef B200_LAUNCH
 }
 }  // namespace
+
+int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream) {
+    if (q.tokens == 0) return 0;
+    if (!q.x || !q.w || !q.row_scales || !q.col_scales || !q.rope_cos || !q.rope_sin || !q.q || !q.k || !q.v ||
+        q.tokens < 0 || q.k_dim <= 0 || q.n_heads <= 0 || q.n_kv_heads <= 0)
+        return fail("invalid linear_qkv_heads arguments tokens=%d K=%d heads=%d/%d", q.tokens, q.k_dim, q.n_heads,
+                    q.n_kv_heads);
+    if (q.d_head != kHeadDim)
+        return fail("the fused QKV epilogue is built for d_head = %d, got %d (use gemm_i8_i32 + qkv_rms_rope_dequant)",
+                    kHeadDim, q.d_head);
+    const void *al[] = {q.col_scales, q.rope_cos, q.rope_sin, q.q, q.k, q.v};
+    for (const void *ptr : al)
+        if (!aligned16(ptr)) return fail("linear_qkv_heads needs 16-byte aligned scales, tables and outputs");
+    if (q.bias && !aligned16(q.bias)) return fail("linear_qkv_heads needs a 16-byte aligned bias");
+    LinearArgs a{};
+    a.x = q.x; a.w = q.w; a.w_layout = q.w_layout; a.m = q.tokens; a.k = q.k_dim;
+    a.n = (q.n_heads + 2 * q.n_kv_heads) * kHeadDim;
+    a.row_scales = q.row_scales; a.col_scales = q.col_scales; a.bias = q.bias;
+    a.out = q.q; a.ldo = a.n; a.out_dtype = B200_DT_F32;  // placeholders for the shared argument check
+    a.static_weights = q.static_weights;
+    if (gemm_can_implement(a, true)) return 1;
+    GemmParams p{};
+    p.M = a.m; p.N = a.n; p.K = a.k;
+    p.row_scales = a.row_scales; p.col_scales = a.col_scales; p.bias = a.bias;
+    p.out_dtype = kOutQkvHeads;
+    p.trace = g_trace;
+    p.static_weights = a.static_weights;
+    p.tma_store = 0;
+    p.vec_ok = 1;
+    p.splits = 1;
+    p.q_heads = q.q; p.k_heads = q.k; p.v_heads = q.v;
+    p.rope_cos = q.rope_cos; p.rope_sin = q.rope_sin;
+    p.n_heads = q.n_heads; p.n_kv_heads = q.n_kv_heads; p.head_eps = q.eps;
+    // 256-wide tiles once they fill the machine, else 128-wide ones for twice the CTAs
+    const long long tiles256 = (long long)((a.m + BM - 1) / BM) * ((a.n + 255) / 256);
+    int bn = tiles256 >= device_sms() ? 256 : 128;
+    const int force_bn = g_force_bn & 0xFFFF;
+    if (force_bn == 256 || force_bn == 128) bn = force_bn;
+    if (bn == 256) return launch_bn_g<256, kOutQkvHeads, false, 0>(a, p, 0, stream);
+    return launch_bn_g<128, kOutQkvHeads, false, 0>(a, p, 1, stream);
+}
 
 size_t static_scratch_capacity() { return kStaticScratchBytes; }
 

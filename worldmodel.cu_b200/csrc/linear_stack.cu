@@ -10,6 +10,7 @@
 // Differences by design: the int32 scratch is gone (epilogues read tensor memory), the
 // controller linear is a residual branch, activations are 16-bit, and rows can be walked
 // in bands so a band's intermediates stay in L2 between producer and consumer kernels.
+#include <stdint.h>
 #include <stdio.h>
 
 #include <map>
@@ -268,6 +269,90 @@ int b200_w8a8_stack_set_layer(void *handle, int layer, const float *w_qkv, const
     if (upload_vec(s, &L.g_mlp, g_mlp, s->d)) return 1;
     L.loaded = true;
     return 0;
+}
+
+// Copies one layer record of a packed-weight file (host memory, file order) to the device.
+static int upload_record(Stack *s, Layer &L, const uint8_t *rec) {
+    Weight *ws[5] = {&L.qkv, &L.out, &L.ctrl, &L.up, &L.down};
+    const int ns[5] = {s->n_qkv, s->d, s->d, s->hidden, s->d};
+    const int ks[5] = {s->d, s->d, s->d, s->d, s->hidden};
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < 5 && e == cudaSuccess; ++i) {
+        const size_t cb = packed_weight_bytes(ns[i], ks[i], B200_W_SLAB128), sb = (size_t)ns[i] * sizeof(float);
+        if (!ws[i]->codes) {
+            if (dev_alloc(s, (void **)&ws[i]->codes, cb)) return 1;
+            if (dev_alloc(s, (void **)&ws[i]->scales, sb)) return 1;
+        }
+        ws[i]->n = ns[i];
+        ws[i]->k = ks[i];
+        e = cudaMemcpy(ws[i]->codes, rec, cb, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(ws[i]->scales, rec + cb, sb, cudaMemcpyHostToDevice);
+        rec += cb + sb;
+    }
+    float **gs[3] = {&L.g_attn, &L.g_ctrl, &L.g_mlp};
+    const size_t gb = (size_t)s->d * sizeof(float);
+    for (int i = 0; i < 3 && e == cudaSuccess; ++i) {
+        if (!*gs[i] && dev_alloc(s, (void **)gs[i], gb)) return 1;
+        e = cudaMemcpy(*gs[i], rec, gb, cudaMemcpyHostToDevice);
+        rec += gb;
+    }
+    if (e != cudaSuccess) return fail("CUDA error while copying packed weights: %s", cudaGetErrorString(e));
+    L.loaded = true;
+    return 0;
+}
+
+int b200_w8a8_stack_load_weights(void *handle, const char *path) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s || !path) return fail("invalid stack_load_weights arguments");
+    int d = 0, nq = 0, hid = 0, nl = 0;
+    if (weight_file_info(path, &d, &nq, &hid, &nl, 1)) return 1;
+    if (d != s->d || nq != s->n_qkv || hid != s->hidden || nl != s->n_layers)
+        return fail("%s holds d=%d n_qkv=%d hidden=%d layers=%d, the stack is d=%d n_qkv=%d hidden=%d layers=%d", path,
+                    d, nq, hid, nl, s->d, s->n_qkv, s->hidden, s->n_layers);
+    std::vector<uint8_t> rec(weight_file_layer_bytes(d, nq, hid));
+    for (int l = 0; l < nl; ++l) {
+        if (weight_file_read_layer(path, l, d, nq, hid, rec.data())) return 1;
+        if (upload_record(s, s->layers[(size_t)l], rec.data())) return 1;
+    }
+    return 0;
+}
+
+int b200_w8a8_stack_save_weights(void *handle, const char *path) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s || !path) return fail("invalid stack_save_weights arguments");
+    for (const Layer &L : s->layers)
+        if (!L.loaded) return fail("stack_save_weights called before every layer was loaded");
+    WeightFileWriter *w = weight_file_create(path, s->d, s->n_qkv, s->hidden, s->n_layers);
+    if (!w) return 1;
+    int rc = 0;
+    for (const Layer &L : s->layers) {
+        const Weight *ws[5] = {&L.qkv, &L.out, &L.ctrl, &L.up, &L.down};
+        std::vector<int8_t> codes[5];
+        std::vector<float> scales[5], gammas[3];
+        const int8_t *cp[5];
+        const float *sp[5], *gp[3];
+        cudaError_t e = cudaSuccess;
+        for (int i = 0; i < 5 && e == cudaSuccess; ++i) {
+            codes[i].resize(packed_weight_bytes(ws[i]->n, ws[i]->k, B200_W_SLAB128));
+            scales[i].resize((size_t)ws[i]->n);
+            e = cudaMemcpy(codes[i].data(), ws[i]->codes, codes[i].size(), cudaMemcpyDeviceToHost);
+            if (e == cudaSuccess)
+                e = cudaMemcpy(scales[i].data(), ws[i]->scales, scales[i].size() * sizeof(float), cudaMemcpyDeviceToHost);
+            cp[i] = codes[i].data();
+            sp[i] = scales[i].data();
+        }
+        const float *gd[3] = {L.g_attn, L.g_ctrl, L.g_mlp};
+        for (int i = 0; i < 3 && e == cudaSuccess; ++i) {
+            gammas[i].resize((size_t)s->d);
+            e = cudaMemcpy(gammas[i].data(), gd[i], (size_t)s->d * sizeof(float), cudaMemcpyDeviceToHost);
+            gp[i] = gammas[i].data();
+        }
+        if (e != cudaSuccess) rc = fail("CUDA error while reading back packed weights: %s", cudaGetErrorString(e));
+        if (!rc) rc = weight_file_add_packed(w, cp, sp, gp);
+        if (rc) break;
+    }
+    const int rc_close = weight_file_close(w);
+    return rc ? rc : rc_close;
 }
 
 int b200_w8a8_stack_set_lanes(void *handle, int lanes) {

@@ -77,6 +77,8 @@ int qkv_rms_rope_dequant(const int32_t *qkv_acc, const float *row_scales, const 
                          float *k, float *v, const int64_t *x_pos, const int64_t *y_pos, const int64_t *t_pos,
                          const float *xy, const float *inv_t, int tokens, int n_heads, int n_kv_heads, int d_head,
                          int width, int height, float eps, cudaStream_t stream);
+int rope_tables(const int64_t *x_pos, const int64_t *y_pos, const int64_t *t_pos, const float *xy, const float *inv_t,
+                int tokens, int d_head, int width, int height, float *cos_out, float *sin_out, cudaStream_t stream);
 
 // ---- gemm_i8_tcgen05.cu
 struct LinearArgs {
@@ -98,6 +100,22 @@ struct LinearArgs {
     int static_weights;       // w is never written by work queued on the stream: its first tiles may be
                               // fetched before the predecessor kernel has finished
 };
+// QKV linear with the per-head RMSNorm + rotary consumer as its epilogue (d_head = 64).
+struct QkvHeadsArgs {
+    const int8_t *x;          // A8 codes [tokens, k_dim]
+    const int8_t *w;          // W8 codes [(Hq + 2 Hkv) * 64, k_dim], row-major or slab layout
+    int w_layout;
+    const float *row_scales;  // [tokens]
+    const float *col_scales;  // [(Hq + 2 Hkv) * 64]
+    const float *bias;        // nullable
+    const float *rope_cos;    // [tokens, 32]
+    const float *rope_sin;    // [tokens, 32]
+    float *q, *k, *v;         // head-major fp32 [Hq,T,64], [Hkv,T,64], [Hkv,T,64]
+    int tokens, k_dim, n_heads, n_kv_heads, d_head;
+    float eps;
+    int static_weights;
+};
+int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream);
 int gemm_can_implement(const LinearArgs &a, bool verbose);
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemm_workspace_size(int m, int k, int n);
@@ -111,5 +129,15 @@ void gemm_set_trace_buffer(unsigned long long *dev_buf);
 // ---- pack_weights.cpp
 int pack_weight_host(const float *w, int n, int k, int layout, int8_t *packed, float *scales, int threads);
 size_t packed_weight_bytes(int n, int k, int layout);
+
+// ---- weight_file.cpp (host only)
+struct WeightFileWriter;
+size_t weight_file_layer_bytes(int d, int n_qkv, int hidden);
+WeightFileWriter *weight_file_create(const char *path, int d, int n_qkv, int hidden, int n_layers);
+int weight_file_add_packed(WeightFileWriter *w, const int8_t *const codes[5], const float *const scales[5],
+                           const float *const gammas[3]);
+int weight_file_close(WeightFileWriter *w);
+int weight_file_info(const char *path, int *d, int *n_qkv, int *hidden, int *n_layers, int verify);
+int weight_file_read_layer(const char *path, int layer, int d, int n_qkv, int hidden, void *dst);
 
 }  // namespace b200
