@@ -219,6 +219,12 @@ def run_reference_arm(args):
             "config": {"workload": "cfg1: 24-layer W8A8 linear stack, M=512, d=2048, qkv 6144, mlp 8192, fp16"},
             "cpu_baseline": {"value": tops, "unit": "TOP/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": tops, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    # Beside the CPU figure: the reference's own CUDA operators on this box's GPU, when they were built.
+    try:
+        line["reference_cuda_ops_same_gpu"] = (run_reference_cuda_ops() if torch.cuda.is_available()
+                                               else {"unavailable": "no CUDA device"})
+    except Exception as exc:  # a comparator must never cost the line
+        line["reference_cuda_ops_same_gpu"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     print(json.dumps(line))
     return 0
 
@@ -491,6 +497,141 @@ def run_extras(pkg, ref, stack, stream, peaks):
     ms, _, _ = time_steps(fn, 20, stream, lambda: None)
     out["cfg1_eager_ms_per_step"] = ms / 20
     out["cfg4_skinny"] = run_skinny(pkg, stream, peaks)
+    out["qkv_heads_t512"] = run_qkv_heads(pkg, stream)
+    return out
+
+
+def run_reference_cuda_ops(rows=512, n_heads=32, d_head=64):
+    """The reference's own CUDA operators (src/world_cuda_ops.cu compiled into oracle/_ref/, its
+    CUTLASS Sm80 mma.sync GEMM included) on this GPU: each of the five GEMM shapes into the int32
+    scratch, and the reference's per-layer operator sequence for the linears (norm->A8, GEMM, consumer /
+    dequant kernels; attention left out, as in the stack), with 24 distinct weight sets.  Launched one by
+    one on the default stream like the reference does (its operators take no stream), timed with events."""
+    import torch
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import ref_cuda_ops as rk
+    if not rk.available():
+        return {"unavailable": "oracle/_ref/libworld_cuda_ops_ref.so is not built (needs the reference checkout "
+                               "and a CUTLASS header tree at build time)"}
+    dev = "cuda"
+    d, nq, hid = D_MODEL, N_QKV, D_HIDDEN
+    g = torch.Generator().manual_seed(11)
+    rnd8 = lambda *shape: torch.randint(-127, 128, shape, dtype=torch.int8, device=dev)
+    ws = {name: [rnd8(n, k) for _ in range(N_LAYERS)] for name, n, k in LINEARS}
+    sw = {name: torch.rand(n, device=dev) * 1e-3 for name, n, k in LINEARS}
+    x = torch.randn(rows, d, device=dev)
+    x1, x2, x3 = (torch.empty_like(x) for _ in range(3))
+    gamma = torch.randn(d, device=dev) * 0.05
+    gate = torch.ones(d, device=dev)
+    a8 = rnd8(rows, hid)
+    sa = torch.rand(rows, device=dev) * 1e-2
+    acc = torch.empty(rows, hid, dtype=torch.int32, device=dev)
+    n_kv = (nq // d_head - n_heads) // 2
+    q = torch.empty(n_heads, rows, d_head, device=dev)
+    kk = torch.empty(n_kv, rows, d_head, device=dev)
+    v = torch.empty(n_kv, rows, d_head, device=dev)
+    pos = [torch.randint(0, hi, (rows,), generator=g).to(dev) for hi in (32, 16, 64)]
+    xy = (torch.rand(d_head // 8, generator=g) * 6).to(dev)
+    inv_t = torch.rand(d_head // 2 - 2 * (d_head // 8), generator=g).to(dev)
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3  # us
+
+    out = {"gemm_us": {}}
+    for name, n, k in LINEARS:
+        def gemms(name=name, n=n, k=k):
+            for w in ws[name]:
+                rk.call("gemm_i8_i32", a8, w, acc, rows, k, n)
+        out["gemm_us"][name] = timed(gemms, 3) / N_LAYERS
+
+    def layers():
+        for l in range(N_LAYERS):
+            rk.call("rms_norm_quantize_rows_i8", x, gamma, None, a8, sa, rows, d, 1e-6)
+            rk.call("gemm_i8_i32", a8, ws["qkv"][l], acc, rows, d, nq)
+            rk.call("qkv_fused_rms_rope_i32_dequant", acc, sa, sw["qkv"], q, kk, v, *pos, xy, inv_t, rows, n_heads,
+                    n_kv, d_head, 32, 16, 1e-6)
+            rk.call("quantize_rows_f32_i8", q, a8, sa, rows, d)  # stands in for the attention output [rows, d]
+            rk.call("gemm_i8_i32", a8, ws["out"][l], acc, rows, d, d)
+            rk.call("dequant_gated_residual_f32", acc, sa, sw["out"], x, gate, x1, rows, d)
+            rk.call("rms_norm_quantize_rows_i8", x1, gamma, None, a8, sa, rows, d, 1e-6)
+            rk.call("gemm_i8_i32", a8, ws["ctrl"][l], acc, rows, d, d)
+            rk.call("dequant_add_residual_f32", acc, sa, sw["ctrl"], x1, x2, rows, d)
+            rk.call("rms_norm_quantize_rows_i8", x2, gamma, None, a8, sa, rows, d, 1e-6)
+            rk.call("gemm_i8_i32", a8, ws["up"][l], acc, rows, d, hid)
+            rk.call("dequant_silu_quantize_rows_i8", acc, sa, sw["up"], None, a8, sa, rows, hid)
+            rk.call("gemm_i8_i32", a8, ws["down"][l], acc, rows, hid, d)
+            rk.call("dequant_gated_residual_f32", acc, sa, sw["down"], x2, gate, x3, rows, d)
+    us = timed(layers, 3)
+    out["stack_ms_per_step"] = us / 1e3
+    out["stack_tops"] = rows * OPS_PER_ROW_LAYER * N_LAYERS / (us * 1e-6) / 1e12
+    out["launches_per_layer"] = 14
+    out["note"] = (f"M={rows}, fp32 tokens, SiLU, gated residuals (the reference's operator set); eager launches on the "
+                   "default stream, built with the reference's --use_fast_math")
+    return out
+
+
+def run_qkv_heads(pkg, stream, tokens=512, n_heads=32, n_kv_heads=16, k=2048, d_head=64):
+    """The QKV linear with the per-head RMSNorm + RoPE consumer as its epilogue against the two-call
+    form it replaces (GEMM to int32, then the consumer kernel), the reference's head counts, 24 distinct
+    weight matrices per graph so that weights stream from HBM."""
+    import torch
+    dev = "cuda"
+    n = (n_heads + 2 * n_kv_heads) * d_head
+    g = torch.Generator().manual_seed(7)
+    ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(N_LAYERS)]
+    a8 = torch.randint(-127, 128, (tokens, k), generator=g, dtype=torch.int8).to(dev)
+    sx = (torch.rand(tokens, generator=g) * 0.05 + 0.01).to(dev)
+    sw = (torch.rand(n, generator=g) * 2e-4 + 1e-5).to(dev)
+    pos = [torch.randint(0, hi, (tokens,), generator=g).to(dev) for hi in (32, 16, 64)]
+    xy = (torch.rand(d_head // 8, generator=g) * 6).to(dev)
+    inv_t = torch.rand(d_head // 2 - 2 * (d_head // 8), generator=g).to(dev)
+    acc = torch.empty(tokens, n, dtype=torch.int32, device=dev)
+    q = torch.empty(n_heads, tokens, d_head, device=dev)
+    kk = torch.empty(n_kv_heads, tokens, d_head, device=dev)
+    v = torch.empty(n_kv_heads, tokens, d_head, device=dev)
+    L = pkg.lib()
+    with torch.cuda.stream(stream):
+        cos, sin = pkg.rope_tables(*pos, xy, inv_t, d_head, 32, 16)
+
+    def fused():
+        st = torch.cuda.current_stream().cuda_stream
+        for w in ws:
+            rc = L.b200_w8a8_linear_qkv_heads(a8.data_ptr(), sx.data_ptr(), w.data_ptr(), pkg.W_SLAB128, sw.data_ptr(),
+                                              None, cos.data_ptr(), sin.data_ptr(), q.data_ptr(), kk.data_ptr(),
+                                              v.data_ptr(), tokens, k, n_heads, n_kv_heads, d_head, 1e-6, st)
+            assert rc == 0, L.b200_w8a8_last_error()
+
+    def two_calls():
+        st = torch.cuda.current_stream().cuda_stream
+        for w in ws:
+            rc = L.b200_w8a8_gemm_i8_i32(a8.data_ptr(), w.data_ptr(), pkg.W_SLAB128, acc.data_ptr(), tokens, k, n, st)
+            rc |= L.b200_w8a8_qkv_rms_rope_dequant(acc.data_ptr(), sx.data_ptr(), sw.data_ptr(), q.data_ptr(),
+                                                   kk.data_ptr(), v.data_ptr(), pos[0].data_ptr(), pos[1].data_ptr(),
+                                                   pos[2].data_ptr(), xy.data_ptr(), inv_t.data_ptr(), tokens, n_heads,
+                                                   n_kv_heads, d_head, 32, 16, 1e-6, st)
+            assert rc == 0, L.b200_w8a8_last_error()
+
+    out = {}
+    for name, run in (("fused_us", fused), ("two_call_us", two_calls)):
+        with torch.cuda.stream(stream):
+            run()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run()
+        with torch.cuda.stream(stream):
+            graph.replay()
+        ms, _, _ = time_steps(graph.replay, 5, stream, lambda: None)
+        out[name] = ms / (5 * N_LAYERS) * 1e3
+    out["shape"] = f"T={tokens} K={k} N={n} heads {n_heads}/{n_kv_heads} d_head {d_head}"
     return out
 
 

@@ -8,9 +8,13 @@ Parity pin: the functions below are checked against the reference's own PyTorch 
 test (tools/tests/test_w8a8_quantization.py) both by re-running that file's four known
 answer tests and by golden vectors generated from the reference's private helpers
 (tests/golden/make_golden.py).  The fused operators (RMSNorm->A8, dequant->act->A8,
-dequant->residual, QKV dequant->RMS->RoPE, weight packing) have no runnable pin in the
-reference without the model weights; for those this file restates the cited kernel lines
-and is itself the pin.
+dequant->residual, QKV dequant->RMS->RoPE, weight packing) have no PyTorch pin in the
+reference; for those this file restates the cited kernel lines.  Their runnable pin is the
+reference's own operator file compiled in place (oracle/build_reference_ops.py ->
+oracle/_ref/, loaded by oracle/ref_cuda_ops.py): tests/test_reference_kernels_gpu.py runs
+the reference's eight CUDA operators and this repository's kernels on the same inputs on
+the same GPU (integer results bit for bit, floating-point results within the tolerance
+that the reference's --use_fast_math build leaves).
 
 Conventions fixed here (the reference is not self-consistent between its torch test,
 its probe and its fast-math CUDA build):

@@ -102,3 +102,18 @@ def test_argument_validation_needs_no_gpu(pkg):
     assert lib.b200_w8a8_gemm_i8_i32_can_implement(4096, 8192, 1, 16384, 128, 96, 128) == 1  # slab needs K%128
     assert lib.b200_w8a8_gemm_i8_i32_can_implement(4097, 8192, 0, 16384, 128, 128, 128) == 1  # alignment
     assert lib.b200_w8a8_quantize_rows(None, 0, 8, None, 8, None, 1, 8, None) == 1
+
+
+def test_reference_operator_library_exports_the_eight_w8a8_operators():
+    """oracle/_ref/ holds the reference's own operator file compiled in place (test infrastructure);
+    when it was built, every W8A8 operator must resolve under its C++-mangled name."""
+    import sys
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import ref_cuda_ops as rk
+    if not rk.available():
+        pytest.skip("the reference operator library is not built on this machine")
+    lib = rk.lib()
+    for short in ("gemm_i8_i32", "gemm_i8_i32_can_implement", "quantize_rows_f32_i8", "rms_norm_quantize_rows_i8",
+                  "dequant_silu_quantize_rows_i8", "dequant_gated_residual_f32", "dequant_add_residual_f32",
+                  "qkv_fused_rms_rope_i32_dequant"):
+        assert callable(getattr(lib, short))
