@@ -310,6 +310,9 @@ def main():
     ap.add_argument("--only-gemms", type=int, default=0, metavar="ROWS",
                     help="run the five fused linears of one layer at ROWS rows for --steps rounds with distinct "
                          "weights and exit (a small, self-ending case for ncu captures)")
+    ap.add_argument("--only-qkv-heads", type=int, default=0, metavar="TOKENS",
+                    help="run the QKV linear with the RMSNorm + RoPE epilogue (heads 32/16 x 64) at TOKENS rows for "
+                         "--steps rounds with distinct weights and exit (a small case for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -333,6 +336,8 @@ def main():
     pkg.lib()  # raises if the CUDA library is missing
     if args.only_gemms:
         return run_only_gemms(pkg, args.only_gemms, max(args.steps, 1))
+    if args.only_qkv_heads:
+        return run_only_qkv_heads(pkg, args.only_qkv_heads, max(args.steps, 1))
     peaks = measured_peaks()
     rows, chained, dt_name, band = WORKLOADS[args.workload]
     sharding = _load("w8a8_sharding", ROOT / "worldmodel.cu_b200" / "sharding.py")
@@ -465,6 +470,26 @@ def run_only_gemms(pkg, rows, rounds):
                        const_weights=True)
     torch.cuda.synchronize()
     print(json.dumps({"only_gemms_rows": rows, "rounds": rounds, "status": pkg.poll_status()}))
+    return 0
+
+
+def run_only_qkv_heads(pkg, tokens, rounds, n_heads=32, n_kv_heads=16, d_head=64, k=D_MODEL):
+    import torch
+    dev = "cuda"
+    n = (n_heads + 2 * n_kv_heads) * d_head
+    g = torch.Generator().manual_seed(7)
+    ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(rounds)]
+    a8 = torch.randint(-127, 128, (tokens, k), dtype=torch.int8, device=dev)
+    sx, sw = torch.rand(tokens, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-3
+    pos = [torch.randint(0, hi, (tokens,), generator=g).to(dev) for hi in (32, 16, 64)]
+    xy = (torch.rand(d_head // 8, generator=g) * 6).to(dev)
+    inv_t = torch.rand(d_head // 2 - 2 * (d_head // 8), generator=g).to(dev)
+    cos, sin = pkg.rope_tables(*pos, xy, inv_t, d_head, 32, 16)
+    for w in ws:
+        pkg.linear_qkv_heads(a8, sx, w.view(n, k), sw, cos, sin, n_heads, n_kv_heads, d_head, 1e-6,
+                             w_layout=pkg.W_SLAB128)
+    torch.cuda.synchronize()
+    print(json.dumps({"only_qkv_heads_tokens": tokens, "rounds": rounds, "status": pkg.poll_status()}))
     return 0
 
 
