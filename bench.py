@@ -313,6 +313,9 @@ def main():
     ap.add_argument("--only-qkv-heads", type=int, default=0, metavar="TOKENS",
                     help="run the QKV linear with the RMSNorm + RoPE epilogue (heads 32/16 x 64) at TOKENS rows for "
                          "--steps rounds with distinct weights and exit (a small case for ncu captures)")
+    ap.add_argument("--only-grouped", type=int, default=0, metavar="ROWS",
+                    help="run one grouped call of 24 skinny linears (ROWS rows each, K=2048, N=8192, distinct weights) "
+                         "for --steps rounds and exit (a small case for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -338,6 +341,8 @@ def main():
         return run_only_gemms(pkg, args.only_gemms, max(args.steps, 1))
     if args.only_qkv_heads:
         return run_only_qkv_heads(pkg, args.only_qkv_heads, max(args.steps, 1))
+    if args.only_grouped:
+        return run_only_grouped(pkg, args.only_grouped, max(args.steps, 1))
     peaks = measured_peaks()
     rows, chained, dt_name, band = WORKLOADS[args.workload]
     sharding = _load("w8a8_sharding", ROOT / "worldmodel.cu_b200" / "sharding.py")
@@ -470,6 +475,21 @@ def run_only_gemms(pkg, rows, rounds):
                        const_weights=True)
     torch.cuda.synchronize()
     print(json.dumps({"only_gemms_rows": rows, "rounds": rounds, "status": pkg.poll_status()}))
+    return 0
+
+
+def run_only_grouped(pkg, rows, rounds, k=D_MODEL, n=D_HIDDEN, n_weights=N_LAYERS):
+    import torch
+    dev = "cuda"
+    ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(n_weights)]
+    a8 = torch.randint(-127, 128, (rows, k), dtype=torch.int8, device=dev)
+    sx, sw = torch.rand(rows, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-3
+    probs = [dict(x_i8=a8, x_scales=sx, w_i8=w, w_scales=sw, n=n,
+                  out=torch.empty(rows, n, dtype=torch.float16, device=dev)) for w in ws]
+    for _ in range(rounds):
+        pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
+    torch.cuda.synchronize()
+    print(json.dumps({"only_grouped_rows": rows, "rounds": rounds, "problems": n_weights, "status": pkg.poll_status()}))
     return 0
 
 
@@ -661,7 +681,7 @@ def run_qkv_heads(pkg, stream, tokens=512, n_heads=32, n_kv_heads=16, k=2048, d_
 
 
 def run_skinny(pkg, stream, peaks, n_weights=72):
-    """Config 4: M in {16, 128} rows against K x N int8 weights; a graph-replayed chain of 72 launches
+    """Config 4: M in {16, 32, 64, 128} rows against K x N int8 weights; a graph-replayed chain of 72 launches
     with 72 distinct weight matrices (1.2 GB, far beyond L2); reports weight bytes per second."""
     import torch
     dev = "cuda"
@@ -669,7 +689,7 @@ def run_skinny(pkg, stream, peaks, n_weights=72):
     for k, n in SKINNY_SHAPES:
         ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(n_weights)]
         sw = torch.rand(n, device=dev) * 1e-3
-        for m in (16, 128):
+        for m in (16, 32, 64, 128):
             a8 = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
             sx = torch.rand(m, device=dev) * 1e-2
             y = torch.empty(m, n, dtype=torch.float16, device=dev)
@@ -688,8 +708,26 @@ def run_skinny(pkg, stream, peaks, n_weights=72):
             ms, _, _ = time_steps(graph.replay, 3, stream, lambda: None)
             us = ms / (3 * n_weights) * 1e3
             gbs = (n * k + m * k + 2 * m * n) / us / 1e3
+            # the same 72 linears as independent problems of one grouped call (two launches of <= 48 problems)
+            ys = [torch.empty(m, n, dtype=torch.float16, device=dev) for _ in ws]
+            probs = [dict(x_i8=a8, x_scales=sx, w_i8=w, w_scales=sw, n=n, out=yy) for w, yy in zip(ws, ys)]
+            with torch.cuda.stream(stream):
+                pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
+            stream.synchronize()
+            ggraph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(ggraph, stream=stream):
+                pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
+            with torch.cuda.stream(stream):
+                ggraph.replay()
+            gms, _, _ = time_steps(ggraph.replay, 3, stream, lambda: None)
+            gus = gms / (3 * n_weights) * 1e3
+            ggbs = (n * k + m * k + 2 * m * n) / gus / 1e3
             out[f"m{m}_k{k}_n{n}"] = {"us_per_linear": us, "gb_per_s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                      "frac_of_8000": gbs / 8000.0}
+                                      "frac_of_8000": gbs / 8000.0,
+                                      "grouped_us_per_linear": gus, "grouped_gb_per_s": ggbs,
+                                      "grouped_frac_of_measured_hbm": ggbs / peaks["hbm_gbs"],
+                                      "grouped_frac_of_8000": ggbs / 8000.0}
+            del ys, probs
         del ws
     return out
 

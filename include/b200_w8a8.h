@@ -190,6 +190,29 @@ int b200_w8a8_linear_qkv_heads(const int8_t *x_i8, const float *x_scales, const 
                                const float *rope_sin, float *q, float *k, float *v, int tokens, int k_dim,
                                int n_heads, int n_kv_heads, int d_head, float eps, void *stream);
 
+/* Several independent skinny linears (M <= 128 rows each, own weights, own shapes) in ONE
+ * launch: y_g = act(dequant(x_g @ w_g^T) + bias_g) + residual_g for every problem g.  A single
+ * weight-bound linear leaves HBM idle for most of its 4-5 us of launch, first-byte and
+ * hand-over latency; one persistent kernel that walks the tiles of all problems keeps the
+ * weights of the next problem in flight while the current one finishes.  `problems` is a HOST
+ * array (device pointers inside); w_layout, act and y_dtype are common to the group.
+ * The split-K / stream-K direction the skinny shapes call for: the reference runs each such
+ * linear as its own wm_cuda_gemm_i8_i32 + dequant pair (src/world_cuda.cu:2122-2153). */
+typedef struct {
+    const int8_t *x_i8;     /* [m, k] */
+    const float *x_scales;  /* [m] */
+    const int8_t *w_i8;     /* [n, k] in w_layout */
+    const float *w_scales;  /* [n] */
+    const float *bias;      /* [n] or NULL */
+    const void *residual;   /* [m, ldr] of y_dtype or NULL */
+    int64_t ldr;
+    void *y;                /* [m, ldy] */
+    int64_t ldy;
+    int m, k, n;
+} b200_w8a8_problem;
+int b200_w8a8_linear_grouped(const b200_w8a8_problem *problems_host, int count, int w_layout, int act, int y_dtype,
+                             void *stream);
+
 /* ---- weights (HOST pointers) ------------------------------------------------------ */
 
 /* Per-output-channel symmetric int8 quantization of host fp32 w[N,K] into `layout`,

@@ -40,6 +40,7 @@ _PROTOTYPES = {
     "b200_w8a8_dequant_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                            c_int, c_int, c_void_p]),
     "b200_w8a8_qkv_rms_rope_dequant": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_float, c_void_p]),
+    "b200_w8a8_linear_grouped": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_rope_tables": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p] * 3),
     "b200_w8a8_linear_qkv_heads": (c_int, [c_void_p] * 3 + [c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_void_p]),
     "b200_w8a8_gemm_i8_i32_can_implement": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int]),
@@ -184,6 +185,36 @@ def qkv_rms_rope_dequant(acc, row_scales, w_scales, x_pos, y_pos, t_pos, xy, inv
                                                 n_heads, n_kv_heads, d_head, width, height, eps, _stream()),
            "qkv_rms_rope_dequant")
     return q, k, v
+
+
+class _Problem(ctypes.Structure):
+    """b200_w8a8_problem of include/b200_w8a8.h."""
+    _fields_ = [("x_i8", c_void_p), ("x_scales", c_void_p), ("w_i8", c_void_p), ("w_scales", c_void_p),
+                ("bias", c_void_p), ("residual", c_void_p), ("ldr", ctypes.c_int64), ("y", c_void_p),
+                ("ldy", ctypes.c_int64), ("m", c_int), ("k", c_int), ("n", c_int)]
+
+
+def linear_grouped(problems, w_layout=W_ROW_MAJOR, act=ACT_NONE, out_dtype=None, stream=None):
+    """Runs several independent skinny linears (M <= 128) in one launch.  `problems` is a list of dicts with
+    keys x_i8, x_scales, w_i8, w_scales, n and optionally bias, residual, out; returns the list of outputs."""
+    import torch
+    out_dtype = out_dtype or torch.float16
+    arr = (_Problem * len(problems))()
+    outs = []
+    for i, q in enumerate(problems):
+        m, k = q["x_i8"].shape
+        n = q["n"]
+        res = q.get("residual")
+        y = q.get("out")
+        if y is None:
+            y = torch.empty(m, n, dtype=out_dtype, device=q["x_i8"].device)
+        outs.append(y)
+        arr[i] = _Problem(_ptr(q["x_i8"]), _ptr(q["x_scales"]), _ptr(q["w_i8"]), _ptr(q["w_scales"]), _ptr(q.get("bias")),
+                          _ptr(res), res.stride(0) if res is not None else 0, _ptr(y), y.stride(0), m, k, n)
+    st = stream if stream is not None else _stream()
+    _check(lib().b200_w8a8_linear_grouped(ctypes.cast(arr, c_void_p), len(problems), w_layout, act, _dt(outs[0]) if outs
+                                          else DT_F16, st), "linear_grouped")
+    return outs
 
 
 def rope_tables(x_pos, y_pos, t_pos, xy, inv_t, d_head, width, height):

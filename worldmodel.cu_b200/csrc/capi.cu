@@ -101,6 +101,13 @@ int b200_w8a8_linear_qkv_heads(const int8_t *x_i8, const float *x_scales, const 
     return linear_qkv_heads(a, as_stream(stream));
 }
 
+int b200_w8a8_linear_grouped(const b200_w8a8_problem *problems_host, int count, int w_layout, int act, int y_dtype,
+                             void *stream) {
+    static_assert(sizeof(b200_w8a8_problem) == sizeof(GroupedLinear), "the two problem structs share one layout");
+    return linear_grouped(reinterpret_cast<const GroupedLinear *>(problems_host), count, w_layout, act, y_dtype,
+                          as_stream(stream));
+}
+
 static LinearArgs raw_gemm_args(const int8_t *x, const int8_t *w, int w_layout, const int32_t *acc, int m, int k,
                                 int n) {
     LinearArgs a{};

@@ -1100,6 +1100,193 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
+// ---------------------------------------------------------------- grouped skinny linears (M <= 128)
+// Many independent weight-bound linears in ONE launch.  A single skinny linear cannot use the
+// memory system: its few megabytes of weights stream in well under a microsecond, but launch,
+// first-byte latency, epilogue and hand-over cost four to five.  Here the persistent CTAs walk
+// the 128 x 256 tiles of ALL problems in one sequence, so the operand ring never drains between
+// problems and the weights of problem g+1 are already in flight while the tiles of problem g are
+// being finished.  Every problem has a single block of rows (M <= 128); its A rows are loaded as
+// they are (ceil16(M) rows), the MMA spans 128 lanes and the lanes beyond M are never read back.
+// Problem descriptors and the two tensor maps of each problem travel in kernel-parameter space.
+constexpr int kMaxGroup = 48;  // 48 x (3 tensor maps + 80 bytes) = 22 KB of the 32 KB a kernel may take as parameters
+struct GroupedProblem {
+    const float *row_scales, *col_scales, *bias;
+    const void *residual;
+    void *out;
+    long long ldo, ldr;
+    int m, n, k_blocks;
+    int a_bytes;  // bytes one A copy delivers: ceil16(m) * 128
+    int tile0;    // index of the problem's first tile in the launch-wide sequence
+    int vec_ok;
+    int tma_store;  // the output is aligned for bulk-tensor stores (else plain stores)
+};
+struct GroupedParams {
+    CUtensorMap tm_a[kMaxGroup];
+    CUtensorMap tm_w[kMaxGroup];
+    CUtensorMap tm_out[kMaxGroup];
+    GroupedProblem prob[kMaxGroup];
+    int count, total_tiles, act, out_dtype, w_kx, w_kz;
+};
+
+template <int OUT>
+__global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __grid_constant__ GroupedParams gp) {
+    constexpr int BN = 256;
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *staging = smem + C::kStages * C::kStageBytes;
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(staging + C::kStagingTotal);
+    uint64_t *bar_empty = bar_full + C::kStages;
+    uint64_t *bar_tfull = bar_empty + C::kStages;
+    uint64_t *bar_tempty = bar_tfull + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bar_tfull[b], 1);
+            mbar_init(&bar_tempty[b], kEpilogueWarps);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();
+            int s = 0, g = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int work = blockIdx.x; ok && work < gp.total_tiles; work += gridDim.x) {
+                while (g + 1 < gp.count && work >= gp.prob[g + 1].tile0) ++g;  // tiles are visited in order
+                const GroupedProblem &q = gp.prob[g];
+                const int n0 = (work - q.tile0) * BN;
+                for (int kb = 0; kb < q.k_blocks; ++kb) {
+                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_EMPTY);
+                    if (!ok) break;
+                    uint8_t *sa = smem + s * C::kStageBytes;
+                    mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(q.a_bytes + C::kBBytes));
+                    tma_load_3d(sa, &gp.tm_a[g], &bar_full[s], kb * BK, 0, 0);
+                    tma_load_3d(sa + C::kABytes, &gp.tm_w[g], &bar_full[s], kb * gp.w_kx, n0, kb * gp.w_kz);
+                    if (++s == C::kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_i8(BM, BN);
+            int s = 0, g = 0, t = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int work = blockIdx.x; ok && work < gp.total_tiles; work += gridDim.x, ++t) {
+                while (g + 1 < gp.count && work >= gp.prob[g + 1].tile0) ++g;
+                const int k_blocks = gp.prob[g].k_blocks;
+                const int b = t & 1;
+                const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+                ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_EMPTY);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    ok = mbar_wait_bounded(&bar_full[s], ph, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * C::kStageBytes);
+                    const uint64_t da = umma_smem_desc_k128(sa);
+                    const uint64_t db = umma_smem_desc_k128(sa + C::kABytes);
+#pragma unroll
+                    for (int j = 0; j < BK / 32; ++j)
+                        umma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (uint32_t)((kb | j) != 0));
+                    umma_commit(&bar_empty[s]);
+                    if (++s == C::kStages) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit(&bar_tfull[b]);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const int sub = warp & 3;
+        const int half = ew >> 2;
+        constexpr int kCols = BN / 2;
+        constexpr int kChunks = kCols / 32;
+        uint8_t *stage = staging + ew * C::kWarpStaging;
+        pdl_wait();
+        int t = 0, g = 0, seq = 0;
+        bool ok = true;
+        for (int work = blockIdx.x; ok && work < gp.total_tiles; work += gridDim.x, ++t) {
+            while (g + 1 < gp.count && work >= gp.prob[g + 1].tile0) ++g;
+            const GroupedProblem &q = gp.prob[g];
+            // the shared epilogue code takes the single-problem parameter block: fill in what it reads
+            GemmParams p{};
+            p.M = q.m; p.N = q.n;
+            p.row_scales = q.row_scales; p.col_scales = q.col_scales; p.bias = q.bias; p.gate = nullptr;
+            p.residual = q.residual; p.ldr = q.ldr; p.out = q.out; p.ldo = q.ldo;
+            p.out_dtype = gp.out_dtype; p.act = gp.act; p.vec_ok = q.vec_ok; p.tma_store = q.tma_store;
+            const int b = t & 1;
+            const uint32_t tph = (uint32_t)(t >> 1) & 1u;
+            const int row0 = sub * 32;
+            const int colbase = (work - q.tile0) * BN + half * kCols;
+            float row_scale = 0.0f;
+            if (row0 + lane < p.M) row_scale = __ldg(p.row_scales + row0 + lane);
+            ok = mbar_wait_bounded(&bar_tfull[b], tph, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (row0 < p.M) {  // a sub-partition whose 32 lanes all lie beyond M has nothing to write
+                const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * BN + half * kCols);
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    const int col0 = colbase + c * 32;
+                    if (col0 >= p.N) break;
+                    uint32_t r[32];
+                    uint4 res[4];
+                    tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
+                    fetch_residual16<OUT>(p, row0 + lane, col0, res);
+                    tmem_ld_wait();
+                    epilogue_chunk<OUT, true>(p, &gp.tm_out[g], stage, r, res, lane, row0, col0, row_scale, seq++);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_tempty[b]);
+        }
+        // the staging blocks must outlive the bulk stores that read them
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        __syncwarp();
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1511,6 +1698,79 @@ int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream) {
     if (force_bn == 256 || force_bn == 128) bn = force_bn;
     if (bn == 256) return launch_bn_g<256, kOutQkvHeads, false, 0>(a, p, 0, stream);
     return launch_bn_g<128, kOutQkvHeads, false, 0>(a, p, 1, stream);
+}
+
+int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int act, int out_dtype,
+                   cudaStream_t stream) {
+    if (count == 0) return 0;
+    if (!problems || count < 0) return fail("invalid linear_grouped arguments count=%d", count);
+    if (out_dtype != B200_DT_F32 && out_dtype != B200_DT_F16 && out_dtype != B200_DT_BF16)
+        return fail("linear_grouped: unsupported output dtype %d", out_dtype);
+    if (act < 0 || act > 2) return fail("linear_grouped: unknown activation %d", act);
+    if (w_layout != B200_W_SLAB128 && w_layout != B200_W_ROW_MAJOR) return fail("linear_grouped: unknown weight layout");
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
+    DeviceInfo &di = device_info(dev);
+    using C = Cfg<256>;
+    static bool attr_set[64][3] = {};
+    const int oi = out_dtype == B200_DT_F32 ? 0 : (out_dtype == B200_DT_F16 ? 1 : 2);
+    if (!attr_set[dev & 63][oi]) {
+        cudaError_t e = cudaSuccess;
+        if (oi == 0) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (oi == 1) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (oi == 2) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute(grouped, smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
+        attr_set[dev & 63][oi] = true;
+    }
+    const size_t esz = out_dtype == B200_DT_F32 ? 4 : 2;
+    static thread_local GroupedParams gp;  // 16 KB: kept off the stack
+    for (int first = 0; first < count; first += kMaxGroup) {
+        const int n_here = count - first < kMaxGroup ? count - first : kMaxGroup;
+        gp.count = n_here; gp.act = act; gp.out_dtype = out_dtype;
+        gp.w_kx = w_layout == B200_W_SLAB128 ? 0 : BK;
+        gp.w_kz = w_layout == B200_W_SLAB128 ? 1 : 0;
+        int tiles = 0;
+        for (int i = 0; i < n_here; ++i) {
+            const GroupedLinear &q = problems[first + i];
+            if (!q.x || !q.w || !q.row_scales || !q.col_scales || !q.out || q.m <= 0 || q.n <= 0 || q.k <= 0)
+                return fail("linear_grouped: invalid problem %d (M=%d K=%d N=%d)", first + i, q.m, q.k, q.n);
+            if (q.m > BM) return fail("linear_grouped takes M <= %d rows per problem, problem %d has %d", BM, first + i, q.m);
+            if ((q.k & 31) != 0 || (w_layout == B200_W_SLAB128 && (q.k % BK) != 0))
+                return fail("linear_grouped: problem %d: K=%d must be a multiple of 32 (128 for the slab layout)", first + i, q.k);
+            if (!aligned16(q.x) || !aligned16(q.w)) return fail("linear_grouped: problem %d: x and w must be 16-byte aligned", first + i);
+            if (q.ldo < q.n || (q.residual && q.ldr < q.n)) return fail("linear_grouped: problem %d: row stride smaller than N", first + i);
+            const int a_rows = ((q.m + 15) / 16) * 16;
+            GroupedProblem &d = gp.prob[i];
+            d.row_scales = q.row_scales; d.col_scales = q.col_scales; d.bias = q.bias;
+            d.residual = q.residual; d.out = q.out; d.ldo = q.ldo; d.ldr = q.ldr;
+            d.m = q.m; d.n = q.n; d.k_blocks = (q.k + BK - 1) / BK;
+            d.a_bytes = a_rows * BK;
+            d.tile0 = tiles;
+            d.vec_ok = (!q.residual || (aligned16(q.residual) && ((q.ldr * esz) % 16 == 0))) && aligned16(q.col_scales) &&
+                       (!q.bias || aligned16(q.bias));
+            tiles += (q.n + 255) / 256;
+            d.tma_store = aligned16(q.out) && ((q.ldo * esz) % 16 == 0);
+            memset(&gp.tm_out[i], 0, sizeof(CUtensorMap));
+            if (d.tma_store && make_out_map(&gp.tm_out[i], q.out, out_dtype, (uint64_t)q.n, (uint64_t)q.m, (uint64_t)q.ldo))
+                return 1;
+            const uint64_t K = (uint64_t)q.k;
+            if (make_map(&gp.tm_a[i], q.x, K, (uint64_t)q.m, 1, K, K * (uint64_t)q.m, (uint32_t)a_rows)) return 1;
+            if (w_layout == B200_W_SLAB128) {
+                if (make_map(&gp.tm_w[i], q.w, BK, (uint64_t)q.n, (uint64_t)(q.k / BK), BK, (uint64_t)q.n * BK, 256)) return 1;
+            } else {
+                if (make_map(&gp.tm_w[i], q.w, K, (uint64_t)q.n, 1, K, K * (uint64_t)q.n, 256)) return 1;
+            }
+        }
+        gp.total_tiles = tiles;
+        const int grid = tiles < di.sms ? tiles : di.sms;
+        cudaError_t le;
+        if (oi == 0) le = launch_kernel(gemm_i8_grouped_kernel<B200_DT_F32>, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, stream, gp);
+        else if (oi == 1) le = launch_kernel(gemm_i8_grouped_kernel<B200_DT_F16>, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, stream, gp);
+        else le = launch_kernel(gemm_i8_grouped_kernel<B200_DT_BF16>, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, stream, gp);
+        if (le != cudaSuccess) return fail("launching gemm_i8_grouped: %s", cudaGetErrorString(le));
+        if (check_launch("gemm_i8_grouped")) return 1;
+    }
+    return 0;
 }
 
 size_t static_scratch_capacity() { return kStaticScratchBytes; }

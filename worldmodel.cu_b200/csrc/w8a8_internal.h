@@ -116,6 +116,22 @@ struct QkvHeadsArgs {
     int static_weights;
 };
 int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream);
+// One of several independent skinny linears (M <= 128) run by a single launch; the exported
+// b200_w8a8_problem has the same fields in the same order.
+struct GroupedLinear {
+    const int8_t *x;          // A8 codes [m, k]
+    const float *row_scales;  // [m]
+    const int8_t *w;          // W8 codes in the layout of the call
+    const float *col_scales;  // [n]
+    const float *bias;        // [n], nullable
+    const void *residual;     // [m, ldr] in the output type, nullable
+    long long ldr;
+    void *out;                // [m, ldo]
+    long long ldo;
+    int m, k, n;
+};
+int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int act, int out_dtype,
+                   cudaStream_t stream);
 int gemm_can_implement(const LinearArgs &a, bool verbose);
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemm_workspace_size(int m, int k, int n);
