@@ -1346,6 +1346,7 @@ struct DeviceInfo {
     int sms = 0;
     bool attr_set[3][5][4] = {};
     bool pair_attr_set[4] = {};
+    bool grouped_attr_set[3] = {};
 };
 DeviceInfo &device_info(int dev) {
     static DeviceInfo info[64];
@@ -1712,15 +1713,14 @@ int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int a
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     DeviceInfo &di = device_info(dev);
     using C = Cfg<256>;
-    static bool attr_set[64][3] = {};
     const int oi = out_dtype == B200_DT_F32 ? 0 : (out_dtype == B200_DT_F16 ? 1 : 2);
-    if (!attr_set[dev & 63][oi]) {
+    if (!di.grouped_attr_set[oi]) {
         cudaError_t e = cudaSuccess;
         if (oi == 0) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (oi == 1) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (oi == 2) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute(grouped, smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
-        attr_set[dev & 63][oi] = true;
+        di.grouped_attr_set[oi] = true;
     }
     const size_t esz = out_dtype == B200_DT_F32 ? 4 : 2;
     static thread_local GroupedParams gp;  // 16 KB: kept off the stack
