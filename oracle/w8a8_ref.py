@@ -236,7 +236,7 @@ def w8a8_linear_reference(x: torch.Tensor, weight: torch.Tensor):
 
 
 # --------------------------------------------------------------------------------------
-# synthetic workloads (BASELINE configs) and the 24-layer linear stack
+# synthetic workloads (the benchmark configurations) and the 24-layer linear stack
 # --------------------------------------------------------------------------------------
 D_MODEL = 2048
 N_QKV = 6144
