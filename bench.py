@@ -313,6 +313,9 @@ def main():
     ap.add_argument("--only-qkv-heads", type=int, default=0, metavar="TOKENS",
                     help="run the QKV linear with the RMSNorm + RoPE epilogue (heads 32/16 x 64) at TOKENS rows for "
                          "--steps rounds with distinct weights and exit (a small case for ncu captures)")
+    ap.add_argument("--only-quant", type=int, default=0, metavar="ROWS",
+                    help="run the three quantizers of a layer (RMSNorm->A8 of fp16 rows, A8 of the first 2048 of 6144 "
+                         "fp16 columns, A8 of 8192 fp32 columns) at ROWS rows for --steps rounds and exit")
     ap.add_argument("--only-grouped", type=int, default=0, metavar="ROWS",
                     help="run one grouped call of 24 skinny linears (ROWS rows each, K=2048, N=8192, distinct weights) "
                          "for --steps rounds and exit (a small case for ncu captures)")
@@ -343,6 +346,8 @@ def main():
         return run_only_qkv_heads(pkg, args.only_qkv_heads, max(args.steps, 1))
     if args.only_grouped:
         return run_only_grouped(pkg, args.only_grouped, max(args.steps, 1))
+    if args.only_quant:
+        return run_only_quant(pkg, args.only_quant, max(args.steps, 1))
     peaks = measured_peaks()
     rows, chained, dt_name, band = WORKLOADS[args.workload]
     sharding = _load("w8a8_sharding", ROOT / "worldmodel.cu_b200" / "sharding.py")
@@ -475,6 +480,22 @@ def run_only_gemms(pkg, rows, rounds):
                        const_weights=True)
     torch.cuda.synchronize()
     print(json.dumps({"only_gemms_rows": rows, "rounds": rounds, "status": pkg.poll_status()}))
+    return 0
+
+
+def run_only_quant(pkg, rows, rounds):
+    import torch
+    dev = "cuda"
+    x = torch.randn(rows, D_MODEL, device=dev).half()
+    gamma = 1 + 0.05 * torch.randn(D_MODEL, device=dev)
+    qkv = torch.randn(rows, N_QKV, device=dev).half()
+    h = torch.randn(rows, D_HIDDEN, device=dev)
+    for _ in range(rounds):
+        pkg.rms_norm_quantize_rows(x, gamma, None, 1e-6, scale_is_mod=False)
+        pkg.quantize_rows(qkv, cols=D_MODEL)
+        pkg.quantize_rows(h)
+    torch.cuda.synchronize()
+    print(json.dumps({"only_quant_rows": rows, "rounds": rounds}))
     return 0
 
 
