@@ -45,10 +45,23 @@ extern "C" {
 int b200_w8a8_abi_version(void);
 /* Last failure message of the calling thread ("" if none). */
 const char *b200_w8a8_last_error(void);
-/* Synchronises the current device and reports the status word GEMM kernels leave when one
- * of their bounded waits ran out (0 = healthy; see KernelStatus in csrc/common.cuh).
- * The reference has no counterpart: its kernels have no device-side waits. */
+/* Every device-side wait of the GEMM kernels has a time limit (2 s).  A kernel whose wait runs out
+ * drains, exits and leaves a code in a status word kept in pinned host memory that the device writes
+ * directly; the next call of any launching entry point (the wm_cuda_* operators included) sees it with
+ * a plain host load, prints the reason, returns 1 once and starts clean (it synchronizes the device,
+ * clears the word and re-zeroes the ticket counters of the built-in split-K scratch; a split-K
+ * workspace owned by the caller must be zeroed again by the caller).  That is the reference's
+ * "non-zero on any failure" convention (src/world_cuda_ops.cu:28-42, 2856-2863) extended to
+ * failures a kernel discovers after its launch returned.
+ * b200_w8a8_poll_status synchronizes the current device and reports and clears the word
+ * (0 = healthy; codes: KernelStatus in csrc/common.cuh). */
 int b200_w8a8_poll_status(int *status_out);
+/* Test aids for the failure path (no counterpart in the reference).  set_wait_limit_ns changes the
+ * limit of every later launch (0 restores 2 s).  drop_operand_load makes the TMA producer of the next
+ * `launches` GEMM launches leave out its first activation tile, so that the MMA issuer's wait runs
+ * out and the abort path executes; nothing faults, the kernel returns with status 102. */
+void b200_w8a8_debug_set_wait_limit_ns(unsigned long long ns);
+void b200_w8a8_debug_drop_operand_load(int launches);
 
 /* ---- activation quantizers ------------------------------------------------------- */
 
@@ -110,6 +123,11 @@ int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, 
  * the reference, whose tile shape is a compile-time template argument
  * (src/world_cuda_ops.cu:529-548). */
 void b200_w8a8_set_tile_width(int bn);
+/* Test aid: forces tile width (256/128/64, 0 = planner), the number of K ranges (0 = planner,
+ * 1 = none) and how their partial sums meet (1 = global workspace, 2 = shared memory of a thread-block
+ * cluster) for every later launch; (0, 0, 0) restores the planner.  Not thread-safe by design: set it
+ * from the only thread that launches. */
+void b200_w8a8_debug_force_plan(int tile_width, int k_splits, int split_mode);
 /* Tuning aid: 0 = the planner decides when two CTAs share one 256 x 256 tile (cta_group::2 MMA),
  * 1 = whenever the launch allows it (M > 128, unsplit 256-wide tiles, aligned buffers,
  * N % 32 == 0), 2 = never.  No counterpart in the reference. */
@@ -119,11 +137,11 @@ void b200_w8a8_set_pair_mma(int mode);
  * stream is still finishing, and waits on the device before it touches dependent data; off
  * gives classic full serialization, for A/B timing.  No counterpart in the reference. */
 void b200_w8a8_set_overlapped_launch(int on);
-/* Tuning aid: when dev_buf is non-NULL every later GEMM launch writes nanosecond timestamps
- * per CTA (0 entry, 1 pipeline start, 2 first operands landed, 3 last MMA issued, 4 first
- * accumulator ready, 5 last epilogue done, 6 exit, 8-10 cluster split-K phases) into the
- * device buffer dev_buf[grid][16] of uint64.  NULL switches it off.  No counterpart in the
- * reference. */
+/* Tuning aid, active only in a library built with -DB200_TRACE (the default build compiles the
+ * timestamps out and ignores the buffer): every later GEMM launch writes nanosecond timestamps per
+ * CTA (0 entry, 1 pipeline start, 2 first operands landed, 3 last MMA issued, 4 first accumulator
+ * ready, 5 last epilogue done, 6 exit, 8-10 cluster split-K phases) into dev_buf[grid][16] of uint64.
+ * No counterpart in the reference. */
 void b200_w8a8_set_trace_buffer(void *dev_buf);
 
 /* One fused linear: y = store( residual + gate * act( acc * x_scales[r] * w_scales[c] + bias[c] ) )
@@ -147,6 +165,32 @@ int b200_w8a8_linear_const_weights(const int8_t *x_i8, const float *x_scales, co
                                    const float *w_scales, const float *bias, const float *gate,
                                    const void *residual, int64_t ldr, void *y, int y_dtype, int64_t ldy, int m,
                                    int k, int n, int act, void *workspace, size_t workspace_bytes, void *stream);
+
+/* A fused linear that also emits the NEXT linear's activation codes from its epilogue:
+ *   y      = store( residual + gate * act( acc * x_scales[r] * w_scales[c] + bias[c] ) )   (y may be NULL)
+ *   q, q_scales = per-row absmax int8 of y[:, 0:q_cols]                       (q_mode B200_RQ_PLAIN)
+ *              or of RMSNorm(y[:, 0:q_cols], eps) * norm_scale + norm_bias     (q_mode B200_RQ_RMS;
+ *                 norm_scale / norm_bias nullable, scale_is_mod = 1 multiplies by 1 + norm_scale)
+ * computed on the values as stored in y_dtype (fp32 when y is NULL and y_dtype is fp32), so q and
+ * q_scales are bit-identical to b200_w8a8_quantize_rows / b200_w8a8_rms_norm_quantize_rows run on y.
+ * One launch replaces the reference's dequant kernel plus the following quantizer:
+ * wm_cuda_dequant_gated_residual_f32 / wm_cuda_dequant_add_residual_f32 followed by
+ * wm_cuda_rms_norm_quantize_rows_i8 (src/world_cuda.cu:2088-2120, 2146-2196, 2322-2330 with the next
+ * layer's :1820-1828), wm_cuda_dequant_silu_quantize_rows_i8 (src/world_cuda_ops.cuh:31-39,
+ * src/world_cuda.cu:2129-2137) and wm_cuda_quantize_rows_f32_i8 on a column block of the result.
+ * A row's q_cols columns are spread over q_cols / 256 CTAs of one thread-block cluster, which
+ * exchange the row statistics through distributed shared memory: q_cols must be a multiple of
+ * 256 and at most 2048; N a multiple of 32; all buffers 16-byte aligned with ldq % 16 == 0. */
+#define B200_RQ_PLAIN 1
+#define B200_RQ_RMS 2
+int b200_w8a8_linear_requant(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
+                             const float *w_scales, const float *bias, const float *gate, const void *residual,
+                             int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
+                             int q_mode, int q_cols, const float *norm_scale, int scale_is_mod,
+                             const float *norm_bias, float eps, int8_t *q, int64_t ldq, float *q_scales,
+                             void *stream);
+/* 0 when b200_w8a8_linear_requant can run this shape / alignment, else 1 (no message). */
+int b200_w8a8_linear_requant_supported(int m, int k, int n, int q_cols);
 
 /* The fused linear for callers that must not allocate device memory: code running under a
  * memory budget that is fixed at start-up, inside a region where the allocator may not be
@@ -260,6 +304,12 @@ int b200_w8a8_stack_forward_host(void *stack, const void *x_host, void *y_host, 
  * one stream (CMakeLists.txt:46); rows of different bands never interact, so results are
  * unchanged. */
 int b200_w8a8_stack_set_lanes(void *stack, int lanes);
+/* on = 1 (default): the out, controller and down linears and the Q block of the QKV linear emit the
+ * next linear's activation codes from their own epilogue (b200_w8a8_linear_requant), six launches per
+ * layer; on = 0: every quantizer is its own launch, ten per layer, the reference's call structure
+ * (src/world_cuda.cu:1819-2330).  Results are bit-identical either way.  The fused form needs
+ * d_model % 256 == 0 and d_model <= 2048; other widths always take the ten-launch form. */
+int b200_w8a8_stack_set_fusion(void *stack, int on);
 /* Switches the 16-bit activation type (fp16 <-> bf16) of later forwards; both are 2 bytes,
  * so buffers are kept and only cached graphs are dropped. */
 int b200_w8a8_stack_set_act_dtype(void *stack, int act_dtype);

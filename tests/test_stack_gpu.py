@@ -69,17 +69,21 @@ def test_each_operator_of_a_layer_against_the_oracle_on_the_same_inputs(pkg, ref
     assert same(c["x3"], ref.linear_w8a8(c["q5"], c["s5"], *lw.down, residual=c["x2"], out_dtype=dtype))
 
 
+@pytest.mark.parametrize("fusion", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("rows,band,steps,graph,lanes", [(200, 0, 1, False, 1), (200, 128, 2, False, 1),
                                                          (333, 0, 2, True, 1), (16, 0, 1, True, 1),
                                                          (333, 64, 1, False, 2), (333, 96, 2, True, 2)])
-def test_stack_driver_equals_operator_composition(pkg, ref, dtype, rows, band, steps, graph, lanes):
+def test_stack_driver_equals_operator_composition(pkg, ref, dtype, rows, band, steps, graph, lanes, fusion):
+    """fusion=True: the quantizers that follow a linear run inside that linear's epilogue (six launches per
+    layer plus the first norm); fusion=False: the ten-launch form.  Both must equal the composition."""
     n_layers = 3
     layers_fp32 = [ref.make_layer_fp32(l, D, NQKV, HID) for l in range(n_layers)]
     stack = pkg.LinearStack(D, NQKV, HID, n_layers, max_rows=rows, band_rows=band, dtype=dtype)
     for l, (ws, gs) in enumerate(layers_fp32):
         stack.set_layer(l, ws, gs, threads=4)
     stack.set_lanes(lanes)  # two lanes: alternate bands run on two streams
+    stack.set_fusion(fusion)
     Ls = [dev_layer(pkg, ref.make_layer(l, D, NQKV, HID)) for l in range(n_layers)]
     x = ref.make_tokens(rows, 1, dtype, D).to(DEV)
     want = x
@@ -93,7 +97,8 @@ def test_stack_driver_equals_operator_composition(pkg, ref, dtype, rows, band, s
     stream.synchronize()
     assert pkg.poll_status() == 0
     assert same(y, want) and same(y2, want)
-    assert stack.launches_per_forward == 10 * n_layers * steps * (1 if band == 0 else -(-rows // band))
+    per_band = (6 * n_layers * steps + 1) if fusion else 10 * n_layers * steps
+    assert stack.launches_per_forward == per_band * (1 if band == 0 else -(-rows // band))
     # host entry point: pinned buffers in, pinned buffers out
     xh = x.cpu().pin_memory()
     yh = torch.empty_like(xh).pin_memory()

@@ -20,6 +20,7 @@ HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libb200_w8a8.so"
 
 DT_F32, DT_F16, DT_BF16, DT_S32 = 0, 1, 2, 3
+RQ_PLAIN, RQ_RMS = 1, 2
 ACT_NONE, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
 W_ROW_MAJOR, W_SLAB128 = 0, 1
 
@@ -45,6 +46,14 @@ _PROTOTYPES = {
     "b200_w8a8_linear_qkv_heads": (c_int, [c_void_p] * 3 + [c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_void_p]),
     "b200_w8a8_gemm_i8_i32_can_implement": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int]),
     "b200_w8a8_gemm_i8_i32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_w8a8_debug_set_wait_limit_ns": (None, [ctypes.c_ulonglong]),
+    "b200_w8a8_debug_drop_operand_load": (None, [c_int]),
+    "b200_w8a8_debug_force_plan": (None, [c_int, c_int, c_int]),
+    "b200_w8a8_linear_requant": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,
+                                         c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int64, c_void_p,
+                                         c_void_p]),
+    "b200_w8a8_linear_requant_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "b200_w8a8_set_tile_width": (None, [c_int]),
     "b200_w8a8_set_trace_buffer": (None, [c_void_p]),
     "b200_w8a8_set_pair_mma": (None, [c_int]),
@@ -67,6 +76,7 @@ _PROTOTYPES = {
     "b200_w8a8_stack_forward_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "b200_w8a8_stack_set_act_dtype": (c_int, [c_void_p, c_int]),
     "b200_w8a8_stack_set_lanes": (c_int, [c_void_p, c_int]),
+    "b200_w8a8_stack_set_fusion": (c_int, [c_void_p, c_int]),
     "b200_w8a8_stack_device_bytes": (c_size_t, [c_void_p]),
     "b200_w8a8_stack_launches_per_forward": (ctypes.c_longlong, [c_void_p]),
     "b200_w8a8_weight_file_create": (c_void_p, [ctypes.c_char_p, c_int, c_int, c_int, c_int]),
@@ -276,6 +286,28 @@ def linear(x_i8, x_scales, w_i8, w_scales, n=None, w_layout=W_ROW_MAJOR, bias=No
     return out
 
 
+def linear_requant(x_i8, x_scales, w_i8, w_scales, n=None, w_layout=W_ROW_MAJOR, bias=None, gate=None, residual=None,
+                   act=ACT_NONE, out_dtype=None, store_out=True, q_mode=RQ_PLAIN, q_cols=None, norm_scale=None,
+                   scale_is_mod=False, norm_bias=None, eps=1e-6):
+    """The fused linear that also emits the next linear's A8 codes (see b200_w8a8_linear_requant).
+    Returns (y or None, codes int8 [m, q_cols], scales fp32 [m])."""
+    import torch
+    m, k = x_i8.shape
+    n = w_scales.shape[0] if n is None else n
+    q_cols = n if q_cols is None else q_cols
+    out_dtype = out_dtype or (residual.dtype if residual is not None else torch.float16)
+    out = torch.empty(m, n, dtype=out_dtype, device=x_i8.device) if store_out else None
+    dt = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}[out_dtype]
+    q = torch.empty(m, q_cols, dtype=torch.int8, device=x_i8.device)
+    qs = torch.empty(m, dtype=torch.float32, device=x_i8.device)
+    _check(lib().b200_w8a8_linear_requant(_ptr(x_i8), _ptr(x_scales), _ptr(w_i8), w_layout, _ptr(w_scales), _ptr(bias),
+                                          _ptr(gate), _ptr(residual), residual.stride(0) if residual is not None else 0,
+                                          _ptr(out), dt, n, m, k, n, act, q_mode, q_cols, _ptr(norm_scale),
+                                          int(scale_is_mod), _ptr(norm_bias), eps, _ptr(q), q_cols, _ptr(qs), _stream()),
+           "linear_requant")
+    return out, q, qs
+
+
 def linear_static_scratch(x_i8, x_scales, w_i8, w_scales, n=None, w_layout=W_ROW_MAJOR, bias=None, gate=None,
                           residual=None, act=ACT_NONE, out=None):
     """The no-allocation entry point: `out` must be supplied, nothing is allocated on the way."""
@@ -377,6 +409,9 @@ class LinearStack:
 
     def set_lanes(self, lanes):
         _check(lib().b200_w8a8_stack_set_lanes(self.handle, lanes), "stack_set_lanes")
+
+    def set_fusion(self, on):
+        _check(lib().b200_w8a8_stack_set_fusion(self.handle, int(bool(on))), "stack_set_fusion")
 
     def set_dtype(self, dtype):
         import torch

@@ -19,9 +19,11 @@ INCLUDE = HERE.parent / "include"
 
 SOURCES = [
     "capi.cu",
+    "status.cu",
     "quant_rows.cu",
     "dequant_ops.cu",
     "gemm_i8_tcgen05.cu",
+    "gemm_i8_rowq.cu",
     "pack_weights.cpp",
     "weight_file.cpp",
     "dropin.cu",

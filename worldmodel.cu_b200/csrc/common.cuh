@@ -17,9 +17,10 @@ enum KernelStatus : int {
     KS_TIMEOUT_SMEM_FULL = 102,   // MMA issuer waited too long for an operand stage
     KS_TIMEOUT_TMEM_EMPTY = 103,  // MMA issuer waited too long for a drained accumulator
     KS_TIMEOUT_TMEM_FULL = 104,   // epilogue waited too long for a finished accumulator
+    KS_TIMEOUT_ROW_EXCHANGE = 105,  // epilogue waited too long for the row statistics of the other CTAs of its cluster
 };
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up
+constexpr unsigned long long kDefaultWaitLimitNs = 2000000000ull;  // 2 s per wait, then give up
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -69,20 +70,65 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Where a bounded wait reports: the CTA-wide abort flag (shared memory), the status word the
+// host reads (device memory, or pinned host memory mapped into the device's address space so
+// that the host sees it without synchronizing) and the time limit of one wait.
+struct WaitCtx {
+    volatile int *abort_flag;
+    int *status;
+    unsigned long long limit_ns;
+};
+
 // Waits for `parity` of `bar` with a time limit.  On expiry it raises the CTA-wide abort
-// flag, records `code` in the device status slot and returns false; it also returns false
-// as soon as another role of the CTA has raised the abort flag.  Nothing ever spins forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                                  int *status_slot, int code) {
+// flag, records `code` in the status word (first code wins) and returns false; it also returns
+// false as soon as another role of the CTA has raised the abort flag.  Nothing ever spins forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, const WaitCtx &w, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if (((++spins) & 0xFFu) == 0) {
-            if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                if (status_slot) atomicCAS(status_slot, 0, code);
+        if (((++spins) & 0x3Fu) == 0) {
+            if (*w.abort_flag) return false;
+            if (global_timer_ns() - t0 > w.limit_ns) {
+                *w.abort_flag = 1;
+                if (w.status) {
+                    volatile int *st = w.status;
+                    if (*st == 0) *st = code;
+                    __threadfence_system();
+                }
+                return false;
+            }
+        }
+    }
+    return true;
+}
+// The same wait on a barrier that CTAs of the cluster signal remotely: acquire at cluster scope,
+// so data the signalling CTAs wrote into this CTA's shared memory before arriving is visible.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t *bar, uint32_t parity, const WaitCtx &w, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    unsigned long long t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if (((++spins) & 0x3Fu) == 0) {
+            if (*w.abort_flag) return false;
+            if (global_timer_ns() - t0 > w.limit_ns) {
+                *w.abort_flag = 1;
+                if (w.status) {
+                    volatile int *st = w.status;
+                    if (*st == 0) *st = code;
+                    __threadfence_system();
+                }
                 return false;
             }
         }

@@ -287,6 +287,9 @@ int qkv_rms_rope_dequant(const int32_t *qkv_acc, const float *row_scales, const 
         return fail("qkv_rms_rope_dequant needs d_head %% 8 == 0 and d_head <= %d, got %d", 64 * kMaxPairsPerLane,
                     d_head);
     if (tokens == 0) return 0;
+    // the kernel reads accumulators and weight scales two at a time
+    if (((reinterpret_cast<uintptr_t>(qkv_acc) | reinterpret_cast<uintptr_t>(weight_scales)) & 7u) != 0)
+        return fail("qkv_rms_rope_dequant needs 8-byte aligned qkv_acc and weight_scales");
     const long long units = (long long)tokens * (n_heads + 2 * n_kv_heads);
     launch_kernel(qkv_rms_rope_dequant_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, stream, qkv_acc,
                   row_scales, weight_scales, q, k, v, x_pos, y_pos, t_pos, xy, inv_t, tokens, n_heads, n_kv_heads,

@@ -3,6 +3,8 @@
 // reference's src/world_cuda_ops.cu makes src/world_cuda.cu call the sm_100a kernels with
 // no source change.  All work goes to the per-thread default stream, which is what the
 // reference's build selects for every launch (CMakeLists.txt:46).
+#include <stdio.h>
+
 #include "../../include/b200_w8a8.h"
 #include "../../include/world_cuda_ops_w8a8.cuh"
 
@@ -25,14 +27,20 @@ int wm_cuda_dequant_silu_quantize_rows_i8(const int32_t *acc, const float *input
 
 int wm_cuda_dequant_gated_residual_f32(const int32_t *acc, const float *row_scales, const float *col_scales,
                                        const float *residual, const float *gate, float *out, int rows, int cols) {
-    if (!residual || !gate) return 1;
+    if (!residual || !gate) {
+        fprintf(stderr, "wm_cuda_dequant_gated_residual_f32: residual and gate must not be NULL\n");
+        return 1;
+    }
     return b200_w8a8_dequant_residual(acc, row_scales, col_scales, residual, B200_DT_F32, gate, out, B200_DT_F32,
                                       rows, cols, B200_STREAM_PER_THREAD);
 }
 
 int wm_cuda_dequant_add_residual_f32(const int32_t *acc, const float *row_scales, const float *col_scales,
                                      const float *residual, float *out, int rows, int cols) {
-    if (!residual) return 1;
+    if (!residual) {
+        fprintf(stderr, "wm_cuda_dequant_add_residual_f32: residual must not be NULL\n");
+        return 1;
+    }
     return b200_w8a8_dequant_residual(acc, row_scales, col_scales, residual, B200_DT_F32, nullptr, out, B200_DT_F32,
                                       rows, cols, B200_STREAM_PER_THREAD);
 }

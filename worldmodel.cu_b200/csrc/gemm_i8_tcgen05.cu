@@ -24,18 +24,11 @@
 //
 // Roofline: tensor-bound for M >= ~1024 (2*M*N*K ops), HBM-bound on the N*K weight bytes
 // for M <= 128.
-#include <cuda.h>
-#include <string.h>
+#include <atomic>
 
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
-#include "w8a8_internal.h"
+#include "gemm_i8_common.cuh"
 
 namespace b200 {
-
-__device__ int g_gemm_status = 0;
 
 // Built-in split-K scratch for callers that cannot allocate device memory (see
 // linear_static_scratch below).  It lives in the module's global segment: every GPU that
@@ -46,335 +39,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 
 namespace {
 
-constexpr int BM = 128;       // rows per tile = TMEM lanes
-constexpr int BK = 128;       // bytes of K per pipeline stage = one swizzle atom
-constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
-constexpr int kSmemBudget = 192 * 1024;          // operand pipeline
-constexpr int kStagingPerWarp = 4096;            // epilogue staging block per warp
-constexpr int kStagingBytes = kEpilogueWarps * kStagingPerWarp;
-
-// WIDE: the QKV-heads epilogue transposes its table reads and its output through shared
-// memory and needs 8 KB per epilogue warp; the operand ring gives up 32 KB for it.
-template <int BN, bool WIDE = false>
-struct Cfg {
-    static constexpr int kABytes = BM * BK;
-    static constexpr int kBBytes = BN * BK;
-    static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kWarpStaging = WIDE ? 2 * kStagingPerWarp : kStagingPerWarp;
-    static constexpr int kStagingTotal = kEpilogueWarps * kWarpStaging;
-    static constexpr int kRing = kSmemBudget - (kStagingTotal - kStagingBytes);
-    static constexpr int kStages = kRing / kStageBytes > 10 ? 10 : kRing / kStageBytes;
-    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingTotal + kBarBytes + 1024;  // + alignment slack
-};
-
-struct GemmParams {
-    int M, N, K;
-    int num_m_blocks, num_n_blocks, num_tiles, num_k_blocks;
-    int group_m;     // m-blocks per raster group (keeps a band of A resident in L2)
-    int splits, kb_per_split, num_work;  // split-K: work item = (tile, K range); num_work = tiles * splits
-    int split_mode;                      // 1 = partials meet in the global workspace, 2 = in cluster shared memory
-    int a_stage_bytes;                   // bytes one A load delivers (fewer than 16 KB when M < 128)
-    int32_t *ws_partials;                // [splits][M][N] raw partial accumulators (split-K only)
-    int *ws_counters;                    // [tiles] arrival tickets, zero between launches
-    int b_kx, b_kz;  // W coordinate multipliers: row-major (128,0), slab layout (0,1)
-    const float *row_scales;
-    const float *col_scales;
-    const float *bias;
-    const float *gate;
-    const void *residual;
-    long long ldr;
-    void *out;
-    long long ldo;
-    int out_dtype;
-    int act;
-    int vec_ok;     // 16-byte vector loads of the per-column vectors / residual are legal
-    int tma_store;  // the output can be written through the TMA store path
-    int static_weights;  // W may be fetched before the predecessor kernel has completed
-    unsigned long long *trace;  // tuning aid: per-CTA timestamps (8 per CTA), or null
-    // QKV consumer epilogue (OUT == kOutQkvHeads only): head-major fp32 outputs and rotary tables
-    float *q_heads, *k_heads, *v_heads;  // [Hq,M,64], [Hkv,M,64], [Hkv,M,64]
-    const float *rope_cos, *rope_sin;    // [M,32]
-    int n_heads, n_kv_heads;
-    float head_eps;
-};
-
-// Pseudo output type of the QKV consumer epilogue: per-head RMSNorm + rotary embedding of Q
-// and K, plain dequantization of V, all written head-major in fp32.
-constexpr int kOutQkvHeads = 4;
-constexpr int kHeadDim = 64;
-
-__device__ __forceinline__ void trace_mark(const GemmParams &p, int slot) {
-    if (p.trace) p.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
-}
-
-__device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &m_blk, int &n_blk);
-// Work item -> (tile, split).  The splits of one tile are adjacent so that they run together.
-__device__ __forceinline__ void decode_work(const GemmParams &p, int work, int &tile, int &m_blk, int &n_blk,
-                                            int &kb0, int &kb1) {
-    const int split = work % p.splits;
-    tile = work / p.splits;
-    decode_tile(p, tile, m_blk, n_blk);
-    kb0 = split * p.kb_per_split;
-    kb1 = min(p.num_k_blocks, kb0 + p.kb_per_split);
-}
-__device__ __forceinline__ void decode_tile(const GemmParams &p, int tile, int &m_blk, int &n_blk) {
-    const int per_group = p.group_m * p.num_n_blocks;
-    const int g = tile / per_group;
-    const int r = tile - g * per_group;
-    const int gm0 = g * p.group_m;
-    const int gsize = min(p.group_m, p.num_m_blocks - gm0);
-    n_blk = r / gsize;
-    m_blk = gm0 + (r - n_blk * gsize);
-}
-
-template <int OUT>
-struct OutElem;
-template <>
-struct OutElem<B200_DT_F16> {
-    static __device__ __forceinline__ uint32_t pack(float a, float b) {
-        __half2 h = __floats2half2_rn(a, b);
-        return *reinterpret_cast<uint32_t *>(&h);
-    }
-    static __device__ __forceinline__ float2 unpack(uint32_t w) {
-        return __half22float2(*reinterpret_cast<const __half2 *>(&w));
-    }
-    static __device__ __forceinline__ float load1(const void *p, long long i) {
-        return __half2float(reinterpret_cast<const __half *>(p)[i]);
-    }
-    static __device__ __forceinline__ void store1(void *p, long long i, float v) {
-        reinterpret_cast<__half *>(p)[i] = __float2half_rn(v);
-    }
-};
-template <>
-struct OutElem<B200_DT_BF16> {
-    static __device__ __forceinline__ uint32_t pack(float a, float b) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-        return *reinterpret_cast<uint32_t *>(&h);
-    }
-    static __device__ __forceinline__ float2 unpack(uint32_t w) {
-        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w));
-    }
-    static __device__ __forceinline__ float load1(const void *p, long long i) {
-        return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
-    }
-    static __device__ __forceinline__ void store1(void *p, long long i, float v) {
-        reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16_rn(v);
-    }
-};
-template <int OUT>
-struct Out16 {
-    static constexpr int value = (OUT == B200_DT_BF16) ? B200_DT_BF16 : B200_DT_F16;
-};
-
-// fp32 epilogue values of 32 consecutive columns of one row from the accumulators in r[]
-// (registers, static indexing only).  Vector form: the chunk lies inside N and 16-byte
-// accesses to the per-column vectors and the residual are legal.
-template <int OUT>
-__device__ __forceinline__ void compute32_vec(const GemmParams &p, const uint32_t (&r)[32], int row, bool row_live,
-                                              int col0, float row_scale, const uint4 (&res16)[4], float (&v)[32]) {
-    {
-        const float4 *cs4 = reinterpret_cast<const float4 *>(p.col_scales + col0);
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            const float4 cs = __ldg(cs4 + g);
-            v[4 * g + 0] = dequant_acc((int)r[4 * g + 0], row_scale, cs.x);
-            v[4 * g + 1] = dequant_acc((int)r[4 * g + 1], row_scale, cs.y);
-            v[4 * g + 2] = dequant_acc((int)r[4 * g + 2], row_scale, cs.z);
-            v[4 * g + 3] = dequant_acc((int)r[4 * g + 3], row_scale, cs.w);
-        }
-    }
-    if (p.bias) {
-        const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + col0);
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            const float4 b = __ldg(b4 + g);
-            v[4 * g + 0] = __fadd_rn(v[4 * g + 0], b.x);
-            v[4 * g + 1] = __fadd_rn(v[4 * g + 1], b.y);
-            v[4 * g + 2] = __fadd_rn(v[4 * g + 2], b.z);
-            v[4 * g + 3] = __fadd_rn(v[4 * g + 3], b.w);
-        }
-    }
-    if (p.act == B200_ACT_GELU_TANH) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = act_gelu_tanh(v[j]);
-    } else if (p.act == B200_ACT_SILU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = act_silu(v[j]);
-    }
-    if (p.gate) {
-        const float4 *g4 = reinterpret_cast<const float4 *>(p.gate + col0);
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            const float4 b = __ldg(g4 + g);
-            v[4 * g + 0] = __fmul_rn(v[4 * g + 0], b.x);
-            v[4 * g + 1] = __fmul_rn(v[4 * g + 1], b.y);
-            v[4 * g + 2] = __fmul_rn(v[4 * g + 2], b.z);
-            v[4 * g + 3] = __fmul_rn(v[4 * g + 3], b.w);
-        }
-    }
-    if (p.residual && row_live) {
-        if (OUT == B200_DT_F32) {
-            const float4 *res = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) +
-                                                                 (long long)row * p.ldr + col0);
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-                const float4 a = res[g];
-                v[4 * g + 0] = __fadd_rn(a.x, v[4 * g + 0]);
-                v[4 * g + 1] = __fadd_rn(a.y, v[4 * g + 1]);
-                v[4 * g + 2] = __fadd_rn(a.z, v[4 * g + 2]);
-                v[4 * g + 3] = __fadd_rn(a.w, v[4 * g + 3]);
-            }
-        } else {
-            constexpr int O = Out16<OUT>::value;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const uint4 raw = res16[g];  // fetched one chunk ahead by the caller
-                float2 f;
-                f = OutElem<O>::unpack(raw.x); v[8 * g + 0] = __fadd_rn(f.x, v[8 * g + 0]); v[8 * g + 1] = __fadd_rn(f.y, v[8 * g + 1]);
-                f = OutElem<O>::unpack(raw.y); v[8 * g + 2] = __fadd_rn(f.x, v[8 * g + 2]); v[8 * g + 3] = __fadd_rn(f.y, v[8 * g + 3]);
-                f = OutElem<O>::unpack(raw.z); v[8 * g + 4] = __fadd_rn(f.x, v[8 * g + 4]); v[8 * g + 5] = __fadd_rn(f.y, v[8 * g + 5]);
-                f = OutElem<O>::unpack(raw.w); v[8 * g + 6] = __fadd_rn(f.x, v[8 * g + 6]); v[8 * g + 7] = __fadd_rn(f.y, v[8 * g + 7]);
-            }
-        }
-    }
-}
-
-// Same arithmetic with every per-column access guarded: ragged right edge or unaligned vectors.
-template <int OUT>
-__device__ __forceinline__ void compute32_guarded(const GemmParams &p, const uint32_t (&r)[32], int row,
-                                                  bool row_live, int col0, float row_scale, float (&v)[32]) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const int col = col0 + j;
-        float t = 0.0f;
-        if (col < p.N) {
-            t = dequant_acc((int)r[j], row_scale, p.col_scales[col]);
-            if (p.bias) t = __fadd_rn(t, p.bias[col]);
-            t = apply_act_rt(t, p.act);
-            if (p.gate) t = __fmul_rn(t, p.gate[col]);
-            if (p.residual && row_live) {
-                const long long ri = (long long)row * p.ldr + col;
-                if (OUT == B200_DT_F32) t = __fadd_rn(reinterpret_cast<const float *>(p.residual)[ri], t);
-                else t = __fadd_rn(OutElem<Out16<OUT>::value>::load1(p.residual, ri), t);
-            }
-        }
-        v[j] = t;
-    }
-}
-
-// Direct stores of one row's 32 values (used when the output cannot be described to TMA).
-template <int OUT>
-__device__ __forceinline__ void store32_direct(const GemmParams &p, const uint32_t (&w)[32], int row, int col0) {
-    // w holds 32-bit words: raw accumulators / fp32 bit patterns, or for 16-bit types the 32 values one per word
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const int col = col0 + j;
-        if (col < p.N) {
-            const long long oi = (long long)row * p.ldo + col;
-            if (OUT == B200_DT_S32 || OUT == B200_DT_F32) reinterpret_cast<uint32_t *>(p.out)[oi] = w[j];
-            else OutElem<Out16<OUT>::value>::store1(p.out, oi, __uint_as_float(w[j]));
-        }
-    }
-}
-
-// One 32-row x 32-column block of the output per call and per warp: every thread writes its
-// row into a swizzled shared-memory staging block, lane 0 hands the block to the TMA store
-// engine, which writes whole row segments and clips at the M / N edges.  A strided per-thread
-// store of the same data costs 32 cache-line transactions per instruction instead.
-template <int OUT>
-__device__ __forceinline__ void stage_and_store(const GemmParams &p, const CUtensorMap *tm_out, uint8_t *stage,
-                                                const uint32_t (&w)[32], int lane, int row0, int col0, int seq) {
-    constexpr bool k32 = (OUT == B200_DT_S32 || OUT == B200_DT_F32);
-    // The warp owns two 2 KB staging blocks of 32 rows x 64 bytes (64-byte swizzle) and alternates
-    // between them, so one bulk store can drain while the next block is being filled.  A 16-bit
-    // chunk (32 columns) is one block; a 32-bit chunk is two blocks of 16 columns.
-    if (k32) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint8_t *buf = stage + h * 2048;
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            __syncwarp();
-            uint8_t *rowp = buf + lane * 64;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4 *>(rowp + ((c ^ ((lane >> 1) & 3)) << 4)) =
-                    make_uint4(w[16 * h + 4 * c], w[16 * h + 4 * c + 1], w[16 * h + 4 * c + 2], w[16 * h + 4 * c + 3]);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                                 tm_out),
-                             "r"(col0 + 16 * h), "r"(row0), "r"(smem_u32(buf))
-                             : "memory");
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-        }
-        return;
-    }
-    uint8_t *buf = stage + (seq & 1) * 2048;
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-    __syncwarp();
-    {
-        constexpr int O = Out16<OUT>::value;
-        uint8_t *rowp = buf + lane * 64;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4 *>(rowp + ((c ^ ((lane >> 1) & 3)) << 4)) = make_uint4(
-                OutElem<O>::pack(__uint_as_float(w[8 * c + 0]), __uint_as_float(w[8 * c + 1])),
-                OutElem<O>::pack(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3])),
-                OutElem<O>::pack(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5])),
-                OutElem<O>::pack(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7])));
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tm_out),
-                     "r"(col0), "r"(row0), "r"(smem_u32(buf))
-                     : "memory");
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    }
-}
-
-// Fetches the 16-bit residual of (row, col0 .. col0+31) into registers; issued one chunk
-// ahead of its use so that the L2 round trip hides behind the previous chunk's arithmetic.
-template <int OUT>
-__device__ __forceinline__ void fetch_residual16(const GemmParams &p, int row, int col0, uint4 (&res16)[4]) {
-    if (OUT == B200_DT_S32 || OUT == B200_DT_F32) return;
-    if (p.residual && p.vec_ok && row < p.M && col0 + 32 <= p.N) {
-        const uint4 *res = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.residual) +
-                                                           (long long)row * p.ldr + col0);
-#pragma unroll
-        for (int g = 0; g < 4; ++g) res16[g] = res[g];
-    }
-}
-
-// GENERAL = false is the lean kernel for the common case (N a multiple of 32, aligned
-// buffers): only the vector arithmetic and the TMA store are compiled in, which keeps the
-// unrolled epilogue small enough to stay resident in the instruction cache.
-template <int OUT, bool GENERAL>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const CUtensorMap *tm_out, uint8_t *stage,
-                                               const uint32_t (&r)[32], const uint4 (&res16)[4], int lane, int row0,
-                                               int col0, float row_scale, int seq) {
-    if (GENERAL && col0 >= p.N) return;  // warp-uniform
-    const int row = row0 + lane;
-    const bool row_live = row < p.M;
-    if (OUT == B200_DT_S32) {
-        if (!GENERAL || p.tma_store) stage_and_store<OUT>(p, tm_out, stage, r, lane, row0, col0, seq);
-        else if (row_live) store32_direct<OUT>(p, r, row, col0);
-        return;
-    }
-    float v[32];
-    if (!GENERAL || (p.vec_ok && col0 + 32 <= p.N)) compute32_vec<OUT>(p, r, row, row_live, col0, row_scale, res16, v);
-    else compute32_guarded<OUT>(p, r, row, row_live, col0, row_scale, v);
-    uint32_t w[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(v[j]);
-    if (!GENERAL || p.tma_store) stage_and_store<OUT>(p, tm_out, stage, w, lane, row0, col0, seq);
-    else if (row_live) store32_direct<OUT>(p, w, row, col0);
-}
+// (tile configuration, parameter block, epilogue arithmetic and tensor-map helpers: gemm_i8_common.cuh)
 
 // QKV consumer as a GEMM epilogue: one thread holds one token's 64 accumulators of one head
 // (two 32-column TMEM loads), so the per-head sum of squares needs no shuffle.  Q and K heads
@@ -512,6 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile int *last_flag = abort_flag + 1;  // split-K: "this CTA holds the last partial of the tile"
+    const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -570,16 +236,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     uint8_t *sa = smem + s * C::kStageBytes;
+                    // test aid: leaving out the very first A tile makes the MMA issuer's wait run out
+                    const bool drop = p.debug_drop_a_load && work == (int)blockIdx.x && kb == kb0;
                     if (prefetched > 0) {
                         // stage already armed and its W tile already requested
                         --prefetched;
-                        tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
+                        if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
                     } else {
-                        ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag, &g_gemm_status,
+                        ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx,
                                                KS_TIMEOUT_SMEM_EMPTY);
                         if (!ok) break;
                         mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(p.a_stage_bytes + C::kBBytes));
-                        tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
+                        if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
                         tma_load_3d(sa + C::kABytes, &tm_b, &bar_full[s], kb * p.b_kx, n0, kb * p.b_kz);
                     }
                     if (++s == C::kStages) { s = 0; ph ^= 1u; }
@@ -603,12 +271,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                 decode_work(p, work, tile, m_blk, n_blk, kb0, kb1);
                 const int b = t & 1;
                 const uint32_t tph = (uint32_t)(t >> 1) & 1u;
-                ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_EMPTY);
+                ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, wctx, KS_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    ok = mbar_wait_bounded(&bar_full[s], ph, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_FULL);
+                    ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     if (t == 0 && kb == kb0) trace_mark(p, 2);
                     tc_fence_after_sync();
@@ -676,8 +344,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                 }
             }
-            ok = mbar_wait_bounded(&bar_tfull[b], tph, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_FULL);
+            ok = mbar_wait_bounded(&bar_tfull[b], tph, wctx, KS_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
+            if (SPLITK == 1) {
+                // the eight warps meet at named barriers below: they go on together or not at all
+                uint32_t all;
+                asm volatile(
+                    "{\n.reg .pred pin, pout;\nsetp.ne.u32 pin, %1, 0;\n"
+                    "barrier.cta.red.and.pred pout, 1, %2, pin;\nselp.u32 %0, 1, 0, pout;\n}"
+                    : "=r"(all)
+                    : "r"((uint32_t)ok), "n"(kEpilogueWarps * 32)
+                    : "memory");
+                ok = all != 0;
+            }
             // (in a cluster every thread still has to meet the cluster barriers; the QKV-heads
             // epilogue first lets the two warps that share a table agree on the outcome)
             if (!ok && SPLITK != 2 && OUT != kOutQkvHeads) break;
@@ -927,6 +606,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint64_t *bar_tempty = bar_tfull + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -972,7 +652,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int m0 = m_blk * 2 * BM + (int)cta_rank * BM;
                 const int n0 = n_blk * BN + (int)cta_rank * (BN / 2);
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_EMPTY);
+                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
                     uint8_t *sa = smem + s * kPairStageBytes;
                     const uint32_t full_in_leader = cluster_map_shared(smem_u32(&bar_full[s]), 0);
@@ -994,12 +674,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++t) {
                 const int b = t & 1;
                 const uint32_t tph = (uint32_t)(t >> 1) & 1u;
-                ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_EMPTY);
+                ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, wctx, KS_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(&bar_full[s], ph, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_FULL);
+                    ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * kPairStageBytes);
@@ -1050,7 +730,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (row0 + lane < p.M) row_scale = __ldg(p.row_scales + row0 + lane);
                 fetch_residual16<OUT>(p, row0 + lane, colbase, res_a);
             }
-            ok = mbar_wait_bounded(&bar_tfull[b], tph, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_FULL);
+            ok = mbar_wait_bounded(&bar_tfull[b], tph, wctx, KS_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
@@ -1127,6 +807,8 @@ struct GroupedParams {
     CUtensorMap tm_out[kMaxGroup];
     GroupedProblem prob[kMaxGroup];
     int count, total_tiles, act, out_dtype, w_kx, w_kz;
+    int *status;
+    unsigned long long wait_limit_ns;
 };
 
 template <int OUT>
@@ -1142,6 +824,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
     uint64_t *bar_tempty = bar_tfull + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const WaitCtx wctx{abort_flag, gp.status, gp.wait_limit_ns};
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -1179,7 +862,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
                 const GroupedProblem &q = gp.prob[g];
                 const int n0 = (work - q.tile0) * BN;
                 for (int kb = 0; kb < q.k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_EMPTY);
+                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
                     uint8_t *sa = smem + s * C::kStageBytes;
                     mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(q.a_bytes + C::kBBytes));
@@ -1201,12 +884,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
                 const int k_blocks = gp.prob[g].k_blocks;
                 const int b = t & 1;
                 const uint32_t tph = (uint32_t)(t >> 1) & 1u;
-                ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_EMPTY);
+                ok = mbar_wait_bounded(&bar_tempty[b], tph ^ 1u, wctx, KS_TIMEOUT_TMEM_EMPTY);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(&bar_full[s], ph, abort_flag, &g_gemm_status, KS_TIMEOUT_SMEM_FULL);
+                    ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * C::kStageBytes);
@@ -1247,7 +930,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
             const int colbase = (work - q.tile0) * BN + half * kCols;
             float row_scale = 0.0f;
             if (row0 + lane < p.M) row_scale = __ldg(p.row_scales + row0 + lane);
-            ok = mbar_wait_bounded(&bar_tfull[b], tph, abort_flag, &g_gemm_status, KS_TIMEOUT_TMEM_FULL);
+            ok = mbar_wait_bounded(&bar_tfull[b], tph, wctx, KS_TIMEOUT_TMEM_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
@@ -1287,75 +970,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
     }
 }
 
-// ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// A byte matrix seen as (inner 128-byte run, rows, slabs) with the 128-byte swizzle.
-int make_map(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1,
-             uint64_t stride2, uint32_t box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[3] = {d0, d1, d2};
-    cuuint64_t strides[2] = {stride1, stride2};
-    cuuint32_t box[3] = {BK, box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS)
-        return fail("cuTensorMapEncodeTiled failed (%d) dims=%llu,%llu,%llu strides=%llu,%llu box_rows=%u", (int)r,
-                    (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2,
-                    (unsigned long long)stride1, (unsigned long long)stride2, box_rows);
-    return 0;
-}
-
-// Output matrix [rows, cols] of 16- or 32-bit elements, written in blocks of 32 rows x 64 bytes
-// whose shared-memory image uses the swizzle that makes a row-per-thread write conflict-free.
-int make_out_map(CUtensorMap *map, const void *base, int dtype, uint64_t cols, uint64_t rows, uint64_t ld) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
-    const bool k32 = dtype == B200_DT_S32 || dtype == B200_DT_F32;
-    const uint64_t esz = k32 ? 4 : 2;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {ld * esz};
-    cuuint32_t box[2] = {k32 ? 16u : 32u, 32};  // 64-byte rows either way
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, k32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
-                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled (output) failed (%d)", (int)r);
-    return 0;
-}
-
-struct DeviceInfo {
-    int sms = 0;
-    bool attr_set[3][5][4] = {};
-    bool pair_attr_set[4] = {};
-    bool grouped_attr_set[3] = {};
-};
-DeviceInfo &device_info(int dev) {
-    static DeviceInfo info[64];
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    DeviceInfo &d = info[dev & 63];
-    if (d.sms == 0) cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
-    return d;
-}
 
 template <int BN, int OUT, bool GENERAL, int SPLITK>
 int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
@@ -1364,12 +978,9 @@ int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t strea
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     DeviceInfo &di = device_info(dev);
     constexpr int kVariant = SPLITK == 2 ? 3 : (SPLITK == 1 ? 2 : (GENERAL ? 1 : 0));
-    if (!di.attr_set[slot][OUT][kVariant]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute(smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
-        di.attr_set[slot][OUT][kVariant] = true;
-    }
+    if (ensure_smem_attr(di.attr_set[slot][OUT][kVariant], gemm_i8_kernel<BN, OUT, GENERAL, SPLITK>, C::kSmemBytes,
+                         "gemm_i8_kernel"))
+        return 1;
     p.num_m_blocks = (a.m + BM - 1) / BM;
     p.num_n_blocks = (a.n + BN - 1) / BN;
     p.num_tiles = p.num_m_blocks * p.num_n_blocks;
@@ -1415,7 +1026,7 @@ int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t strea
     return check_launch("gemm_i8_tcgen05");
 }
 
-int g_pair_mode = 0;  // 0 = planner decides, 1 = whenever legal, 2 = never
+std::atomic<int> g_pair_mode{0};  // 0 = planner decides, 1 = whenever legal, 2 = never
 
 // Launches the CTA-pair kernel: 256 x 256 tiles, lean epilogue only.
 template <int OUT>
@@ -1423,12 +1034,7 @@ int launch_pair(const LinearArgs &a, GemmParams &p, cudaStream_t stream) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     DeviceInfo &di = device_info(dev);
-    if (!di.pair_attr_set[OUT]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_i8_pair_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kPairSmemBytes);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute(pair, smem=%d): %s", kPairSmemBytes, cudaGetErrorString(e));
-        di.pair_attr_set[OUT] = true;
-    }
+    if (ensure_smem_attr(di.pair_attr_set[OUT], gemm_i8_pair_kernel<OUT>, kPairSmemBytes, "gemm_i8_pair_kernel")) return 1;
     p.num_m_blocks = (a.m + 2 * BM - 1) / (2 * BM);  // 256-row pair blocks
     p.num_n_blocks = (a.n + 255) / 256;
     p.num_tiles = p.num_m_blocks * p.num_n_blocks;
@@ -1468,14 +1074,19 @@ int launch_bn(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream)
                 : launch_bn_g<BN, OUT, true, 0>(a, p, slot, stream);
 }
 
-bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
-int g_force_bn = 0;  // tuning override of the tile width (0 = cost model)
-unsigned long long *g_trace = nullptr;  // tuning aid: device buffer for per-CTA timestamps
+// Tuning / test overrides of the planner (process-wide, meant to be set from one thread while no
+// other thread launches): tile width, K-split count and split form; 0 = the cost model decides.
+std::atomic<int> g_force_bn{0}, g_force_splits{0}, g_force_mode{0};
+std::atomic<unsigned long long *> g_trace{nullptr};  // device buffer for per-CTA timestamps (B200_TRACE builds)
 
 }  // namespace
 
-void gemm_set_tile_width(int bn) { g_force_bn = bn; }
+void gemm_set_tile_width(int bn) { gemm_force_plan(bn, 0, 0); }
+void gemm_force_plan(int bn, int splits, int mode) {
+    g_force_bn = bn;
+    g_force_splits = splits;
+    g_force_mode = mode;
+}
 void gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 void gemm_set_trace_buffer(unsigned long long *dev_buf) { g_trace = dev_buf; }
 
@@ -1558,13 +1169,6 @@ Plan make_plan(int m, int k, int n, int sms, bool allow_workspace) {
     return best;
 }
 
-int device_sms() {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int sms = device_info(dev).sms;
-    return sms > 0 ? sms : 148;
-}
-
 }  // namespace
 
 size_t gemm_workspace_size(int m, int k, int n) {
@@ -1575,23 +1179,30 @@ size_t gemm_workspace_size(int m, int k, int n) {
 
 namespace {
 int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream,
-                     const Plan *fixed_plan);
+                     const Plan *fixed_plan, bool may_allocate);
 }
 
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
-    return gemm_launch_impl(a, workspace, workspace_bytes, stream, nullptr);
+    return gemm_launch_impl(a, workspace, workspace_bytes, stream, nullptr, true);
 }
 
 namespace {
+void fill_launch_controls(GemmParams &p, bool may_allocate) {
+    p.trace = g_trace;
+    p.status = status_slot(may_allocate);
+    p.wait_limit_ns = wait_limit_ns();
+    p.debug_drop_a_load = take_debug_drop();
+}
+
 int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream,
-                     const Plan *fixed_plan) {
+                     const Plan *fixed_plan, bool may_allocate) {
     if (gemm_can_implement(a, true)) return 1;
     GemmParams p{};
     p.M = a.m; p.N = a.n; p.K = a.k;
     p.row_scales = a.row_scales; p.col_scales = a.col_scales; p.bias = a.bias; p.gate = a.gate;
     p.residual = a.residual; p.ldr = a.ldr; p.out = a.out; p.ldo = a.ldo;
     p.out_dtype = a.out_dtype; p.act = a.out_dtype == B200_DT_S32 ? 0 : a.act;
-    p.trace = g_trace;
+    fill_launch_controls(p, may_allocate);
     p.static_weights = a.static_weights;
     const size_t esz = (a.out_dtype == B200_DT_S32 || a.out_dtype == B200_DT_F32) ? 4 : 2;
     p.tma_store = aligned16(a.out) && ((a.ldo * esz) % 16 == 0);
@@ -1601,7 +1212,7 @@ int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_byte
 
     const bool ws_ok = workspace && aligned16(workspace);
     Plan pl = make_plan(a.m, a.k, a.n, device_sms(), ws_ok);
-    int force_bn = g_force_bn & 0xFFFF, force_splits = (g_force_bn >> 16) & 0xFF, force_mode = g_force_bn >> 24;
+    int force_bn = g_force_bn, force_splits = g_force_splits, force_mode = g_force_mode;
     if (fixed_plan) {
         force_bn = fixed_plan->bn;
         force_splits = fixed_plan->splits;
@@ -1611,6 +1222,14 @@ int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_byte
     if (force_splits >= 1) {
         pl.splits = force_splits;
         pl.mode = force_splits == 1 ? 0 : (force_mode == 2 ? 2 : 1);
+    }
+    if (pl.mode == 1) {
+        // every K range must hold at least one slab (an empty range would hand the reduction an
+        // accumulator that no MMA wrote): at most 8 ranges, and ceil(kblocks / splits) * (splits - 1) < kblocks
+        const int kblocks = (a.k + BK - 1) / BK;
+        if (pl.splits > 8) pl.splits = 8;
+        while (pl.splits > 1 && ((kblocks + pl.splits - 1) / pl.splits) * (pl.splits - 1) >= kblocks) --pl.splits;
+        if (pl.splits == 1) pl.mode = 0;
     }
     if (pl.mode == 2) {
         const int kblocks = (a.k + BK - 1) / BK;
@@ -1684,8 +1303,8 @@ int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream) {
     p.M = a.m; p.N = a.n; p.K = a.k;
     p.row_scales = a.row_scales; p.col_scales = a.col_scales; p.bias = a.bias;
     p.out_dtype = kOutQkvHeads;
-    p.trace = g_trace;
     p.static_weights = a.static_weights;
+    fill_launch_controls(p, true);
     p.tma_store = 0;
     p.vec_ok = 1;
     p.splits = 1;
@@ -1695,7 +1314,7 @@ int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream) {
     // 256-wide tiles once they fill the machine, else 128-wide ones for twice the CTAs
     const long long tiles256 = (long long)((a.m + BM - 1) / BM) * ((a.n + 255) / 256);
     int bn = tiles256 >= device_sms() ? 256 : 128;
-    const int force_bn = g_force_bn & 0xFFFF;
+    const int force_bn = g_force_bn;
     if (force_bn == 256 || force_bn == 128) bn = force_bn;
     if (bn == 256) return launch_bn_g<256, kOutQkvHeads, false, 0>(a, p, 0, stream);
     return launch_bn_g<128, kOutQkvHeads, false, 0>(a, p, 1, stream);
@@ -1714,19 +1333,16 @@ int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int a
     DeviceInfo &di = device_info(dev);
     using C = Cfg<256>;
     const int oi = out_dtype == B200_DT_F32 ? 0 : (out_dtype == B200_DT_F16 ? 1 : 2);
-    if (!di.grouped_attr_set[oi]) {
-        cudaError_t e = cudaSuccess;
-        if (oi == 0) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (oi == 1) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (oi == 2) e = cudaFuncSetAttribute(gemm_i8_grouped_kernel<B200_DT_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute(grouped, smem=%d): %s", C::kSmemBytes, cudaGetErrorString(e));
-        di.grouped_attr_set[oi] = true;
-    }
+    if (oi == 0 && ensure_smem_attr(di.grouped_attr_set[0], gemm_i8_grouped_kernel<B200_DT_F32>, C::kSmemBytes, "grouped")) return 1;
+    if (oi == 1 && ensure_smem_attr(di.grouped_attr_set[1], gemm_i8_grouped_kernel<B200_DT_F16>, C::kSmemBytes, "grouped")) return 1;
+    if (oi == 2 && ensure_smem_attr(di.grouped_attr_set[2], gemm_i8_grouped_kernel<B200_DT_BF16>, C::kSmemBytes, "grouped")) return 1;
     const size_t esz = out_dtype == B200_DT_F32 ? 4 : 2;
     static thread_local GroupedParams gp;  // 16 KB: kept off the stack
     for (int first = 0; first < count; first += kMaxGroup) {
         const int n_here = count - first < kMaxGroup ? count - first : kMaxGroup;
         gp.count = n_here; gp.act = act; gp.out_dtype = out_dtype;
+        gp.status = status_slot(true);
+        gp.wait_limit_ns = wait_limit_ns();
         gp.w_kx = w_layout == B200_W_SLAB128 ? 0 : BK;
         gp.w_kz = w_layout == B200_W_SLAB128 ? 1 : 0;
         int tiles = 0;
@@ -1807,26 +1423,25 @@ int linear_static_scratch(const LinearArgs &a, cudaStream_t stream) {
     }
     pl.mode = 1;  // this entry point is the workspace form of split-K by definition
     const long long tiles = (long long)((a.m + BM - 1) / BM) * ((a.n + pl.bn - 1) / pl.bn);
-    const size_t need = kCounterBytes + (size_t)pl.splits * (size_t)a.m * (size_t)a.n * sizeof(int32_t);
+    auto scratch_needed = [&](int splits) {
+        return kCounterBytes + (size_t)splits * (size_t)a.m * (size_t)a.n * sizeof(int32_t);
+    };
+    while (pl.splits > 2 && scratch_needed(pl.splits) > kStaticScratchBytes) --pl.splits;  // fewer, longer K ranges
+    const size_t need = scratch_needed(pl.splits);
     if (need > kStaticScratchBytes || tiles > 1024)
         return fail("M=%d N=%d with %d K-splits needs %zu bytes of scratch; the built-in scratch holds %zu "
                     "(use b200_w8a8_linear with a caller-allocated workspace instead)",
                     a.m, a.n, pl.splits, need, kStaticScratchBytes);
-    return gemm_launch_impl(a, scratch, kStaticScratchBytes, stream, &pl);
+    return gemm_launch_impl(a, scratch, kStaticScratchBytes, stream, &pl, false);
 }
 
-int gemm_poll_status(int *status_out) {
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) return fail("cudaDeviceSynchronize: %s", cudaGetErrorString(e));
-    int st = 0;
-    e = cudaMemcpyFromSymbol(&st, g_gemm_status, sizeof(int));
-    if (e != cudaSuccess) return fail("cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
-    if (status_out) *status_out = st;
-    if (st != 0) {
-        int zero = 0;
-        cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
-    }
-    return 0;
+// After a launch that gave up a wait, tiles of a split-K launch may have left tickets behind in
+// the built-in scratch; a later call would then take an early "last ticket".  Caller-owned
+// workspaces are the caller's to zero again.
+void gemm_reset_static_tickets() {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) == cudaSuccess && ptr) cudaMemset(ptr, 0, kCounterBytes);
+    else cudaGetLastError();
 }
 
 }  // namespace b200

@@ -49,10 +49,14 @@ struct Stack {
     struct Scratch {
         int8_t *a8 = nullptr;        // [band, max(d, hidden)]
         float *a8_scales = nullptr;  // [band]
+        int8_t *a8_alt = nullptr;    // second code buffer: a linear that emits the next linear's codes
+        float *a8_alt_scales = nullptr;  // cannot write them over the codes it is still reading
         void *qkv = nullptr;         // [band, n_qkv] 16-bit
         float *h = nullptr;          // [band, hidden] fp32 hidden before re-quantization
     } scratch[2];
     int lanes = 1;
+    int fusion = 1;      // linears with d_model output columns emit the next linear's codes from their epilogue
+    bool fuse_ok = false;  // the shapes allow it (d_model a multiple of 256, at most 2048)
     cudaStream_t lane_stream = nullptr;   // stream of the second lane
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     void *host_stage = nullptr; // device staging for the host entry point
@@ -107,6 +111,58 @@ int fused(const Stack *s, const Weight &w, const int8_t *a8, const float *a8_sca
     return gemm_launch(a, nullptr, 0, stream);
 }
 
+// A fused linear that also emits the codes of the next linear's input (its first d columns,
+// RMS-normalised with `gamma` when given) into q_out / s_out.
+int fused_requant(const Stack *s, const Weight &w, const int8_t *a8, const float *a8_scales, const void *residual,
+                  void *out, long long ldo, const float *gamma, int8_t *q_out, float *s_out, int rows,
+                  cudaStream_t stream) {
+    LinearArgs a{};
+    a.x = a8; a.w = w.codes; a.w_layout = B200_W_SLAB128; a.m = rows; a.k = w.k; a.n = w.n;
+    a.row_scales = a8_scales; a.col_scales = w.scales; a.residual = residual; a.ldr = w.n; a.act = B200_ACT_NONE;
+    a.out = out; a.ldo = ldo; a.out_dtype = s->dtype;
+    a.static_weights = 1;
+    RowQuantSpec qs{};
+    qs.mode = gamma ? B200_RQ_RMS : B200_RQ_PLAIN;
+    qs.cols = s->d; qs.vec_scale = gamma; qs.scale_is_mod = 0; qs.vec_bias = nullptr; qs.eps = s->eps;
+    qs.q = q_out; qs.ldq = s->d; qs.scales = s_out;
+    return linear_requant(a, qs, stream);
+}
+
+// One layer with the four quantizers that follow a linear folded into that linear: six launches
+// instead of ten.  `have_codes` says that the previous layer's down projection already left the
+// RMS-normalised codes of x in the scratch; `next_gamma` (null for the very last layer) is the
+// first norm vector of the layer that follows.  The two code buffers alternate: *cur names the
+// one that holds the current linear's input.
+int layer_band_fused(Stack *s, const Stack::Scratch &w, const Layer &L, const void *x, void *x1, void *x2, void *x3,
+                     int rows, bool have_codes, const float *next_gamma, int *cur, long long *launches,
+                     cudaStream_t st) {
+    const int d = s->d, dt = s->dtype;
+    int8_t *qb[2] = {w.a8, w.a8_alt};
+    float *sb[2] = {w.a8_scales, w.a8_alt_scales};
+    int c = *cur;
+    if (!have_codes) {
+        if (rms_norm_quantize_rows(x, dt, d, L.g_attn, 0, nullptr, qb[c], d, sb[c], rows, d, s->eps, st)) return 1;
+        ++*launches;
+    }
+    if (fused_requant(s, L.qkv, qb[c], sb[c], nullptr, w.qkv, s->n_qkv, nullptr, qb[c ^ 1], sb[c ^ 1], rows, st)) return 1;
+    c ^= 1;
+    if (fused_requant(s, L.out, qb[c], sb[c], x, x1, d, L.g_ctrl, qb[c ^ 1], sb[c ^ 1], rows, st)) return 1;
+    c ^= 1;
+    if (fused_requant(s, L.ctrl, qb[c], sb[c], x1, x2, d, L.g_mlp, qb[c ^ 1], sb[c ^ 1], rows, st)) return 1;
+    c ^= 1;
+    if (fused(s, L.up, qb[c], sb[c], nullptr, B200_ACT_GELU_TANH, w.h, B200_DT_F32, s->hidden, rows, st)) return 1;
+    if (quantize_rows(w.h, B200_DT_F32, s->hidden, qb[c], s->hidden, sb[c], rows, s->hidden, st)) return 1;
+    if (next_gamma) {
+        if (fused_requant(s, L.down, qb[c], sb[c], x2, x3, d, next_gamma, qb[c ^ 1], sb[c ^ 1], rows, st)) return 1;
+        c ^= 1;
+    } else {
+        if (fused(s, L.down, qb[c], sb[c], x2, B200_ACT_NONE, x3, dt, d, rows, st)) return 1;
+    }
+    *launches += 6;
+    *cur = c;
+    return 0;
+}
+
 // The ten operators of one layer on one band of rows of the residual stream.
 int layer_band(Stack *s, const Stack::Scratch &w, const Layer &L, const void *x, void *x1, void *x2, void *x3,
                int rows, cudaStream_t st) {
@@ -145,6 +201,8 @@ int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t 
         const size_t off = (size_t)r0 * row_bytes;
         const void *cur = (const char *)x + off;
         int cur_slot = -1;  // -1: caller's input
+        const bool fuse = s->fusion && s->fuse_ok;
+        int code_buf = 0;
         for (int li = 0; li < total_layers; ++li) {
             const Layer &L = s->layers[li % s->n_layers];
             // Three internal buffers rotate.  x is dead once x1 exists (it is read by the
@@ -158,8 +216,13 @@ int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t 
             const int x3_slot = cur_slot >= 0 ? cur_slot : free_slots[2];
             const bool last = li == total_layers - 1;
             void *x3 = last ? (char *)y + off : (char *)s->tok[x3_slot] + off;
-            if (layer_band(s, w, L, cur, x1, x2, x3, nr, bst)) return 1;
-            launches += 10;
+            if (fuse) {
+                const float *next_gamma = last ? nullptr : s->layers[(li + 1) % s->n_layers].g_attn;
+                if (layer_band_fused(s, w, L, cur, x1, x2, x3, nr, li > 0, next_gamma, &code_buf, &launches, bst)) return 1;
+            } else {
+                if (layer_band(s, w, L, cur, x1, x2, x3, nr, bst)) return 1;
+                launches += 10;
+            }
             cur = x3;
             cur_slot = x3_slot;
         }
@@ -178,6 +241,8 @@ int alloc_scratch(Stack *s, Stack::Scratch *w) {
     const int wide = s->hidden > s->d ? s->hidden : s->d;
     if (dev_alloc(s, (void **)&w->a8, (size_t)s->band_rows * wide)) return 1;
     if (dev_alloc(s, (void **)&w->a8_scales, (size_t)s->band_rows * sizeof(float))) return 1;
+    if (dev_alloc(s, (void **)&w->a8_alt, (size_t)s->band_rows * wide)) return 1;
+    if (dev_alloc(s, (void **)&w->a8_alt_scales, (size_t)s->band_rows * sizeof(float))) return 1;
     if (dev_alloc(s, &w->qkv, (size_t)s->band_rows * s->n_qkv * e)) return 1;
     if (dev_alloc(s, (void **)&w->h, (size_t)s->band_rows * s->hidden * sizeof(float))) return 1;
     return 0;
@@ -205,6 +270,7 @@ void *b200_w8a8_stack_create(int d_model, int n_qkv, int d_hidden, int n_layers,
     s->d = d_model; s->n_qkv = n_qkv; s->hidden = d_hidden; s->n_layers = n_layers; s->max_rows = max_rows;
     s->band_rows = band_rows > 0 && band_rows < max_rows ? band_rows : max_rows;
     s->dtype = act_dtype; s->eps = eps;
+    s->fuse_ok = d_model % 256 == 0 && d_model <= 2048 && n_qkv % 32 == 0;
     s->layers.resize((size_t)n_layers);
     cudaGetDevice(&s->device);
     const size_t e = esize(act_dtype);
@@ -239,6 +305,8 @@ void b200_w8a8_stack_destroy(void *handle) {
     for (auto &w : s->scratch) {
         cudaFree(w.a8);
         cudaFree(w.a8_scales);
+        cudaFree(w.a8_alt);
+        cudaFree(w.a8_alt_scales);
         cudaFree(w.qkv);
         cudaFree(w.h);
     }
@@ -373,6 +441,17 @@ int b200_w8a8_stack_set_lanes(void *handle, int lanes) {
     return 0;
 }
 
+int b200_w8a8_stack_set_fusion(void *handle, int on) {
+    Stack *s = reinterpret_cast<Stack *>(handle);
+    if (!s) return fail("invalid stack_set_fusion");
+    if ((on != 0) != (s->fusion != 0)) {
+        for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);
+        s->graphs.clear();
+        s->fusion = on != 0;
+    }
+    return 0;
+}
+
 int b200_w8a8_stack_set_act_dtype(void *handle, int act_dtype) {
     Stack *s = reinterpret_cast<Stack *>(handle);
     if (!s || (act_dtype != B200_DT_F16 && act_dtype != B200_DT_BF16)) return fail("invalid stack_set_act_dtype");
@@ -397,6 +476,7 @@ long long b200_w8a8_stack_launches_per_forward(void *handle) {
 int b200_w8a8_stack_forward(void *handle, const void *x_dev, void *y_dev, int rows, int steps, int use_graph,
                             void *stream) {
     Stack *s = reinterpret_cast<Stack *>(handle);
+    if (status_check_entry()) return 1;
     if (!s || !x_dev || !y_dev || rows <= 0 || rows > s->max_rows || steps <= 0)
         return fail("invalid stack_forward arguments rows=%d steps=%d", rows, steps);
     for (const Layer &L : s->layers)

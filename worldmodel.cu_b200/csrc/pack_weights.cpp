@@ -70,7 +70,7 @@ int pack_weight_host(const float *w, int n, int k, int layout, int8_t *packed, f
     }
     for (auto &th : pool) th.join();
     if (bad_row.load() >= 0)
-        return fail("non-finite W8 weight at output=%d input=%d for [%d,%d]", bad_row.load(), bad_col.load(), n, k);
+        return fail("weight matrix [%d,%d] holds a value that is not finite at row %d, column %d", n, k, bad_row.load(), bad_col.load());
     return 0;
 }
 

@@ -116,6 +116,23 @@ struct QkvHeadsArgs {
     int static_weights;
 };
 int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream);
+// ---- gemm_i8_rowq.cu: a linear whose epilogue also quantizes the first `cols` columns of its
+// result per row (optionally RMS-normalised first) into the next linear's A8 codes.
+struct RowQuantSpec {
+    int mode;                // B200_RQ_PLAIN / B200_RQ_RMS
+    int cols;                // quantized width: a multiple of 256, at most 2048, at most N
+    const float *vec_scale;  // RMS mode: gamma or modulation [cols], nullable
+    int scale_is_mod;        // 1: multiply by (1 + vec_scale)
+    const float *vec_bias;   // RMS mode: [cols], nullable
+    float eps;
+    int8_t *q;               // [m, ldq] codes
+    long long ldq;
+    float *scales;           // [m]
+};
+// nullptr when the fused form can run these arguments, else the reason it cannot
+const char *linear_requant_unsupported(const LinearArgs &a, const RowQuantSpec &qs);
+// a.out may be null (codes only); a.out_dtype then still names the type the value is rounded to
+int linear_requant(const LinearArgs &a, const RowQuantSpec &qs, cudaStream_t stream);
 // One of several independent skinny linears (M <= 128) run by a single launch; the exported
 // b200_w8a8_problem has the same fields in the same order.
 struct GroupedLinear {
@@ -135,12 +152,26 @@ int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int a
 int gemm_can_implement(const LinearArgs &a, bool verbose);
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemm_workspace_size(int m, int k, int n);
-int gemm_poll_status(int *status_out);
+void gemm_reset_static_tickets();
+
+// ---- status.cu
+// Device-visible address of the status word (pinned host memory mapped into the device when
+// may_allocate allows creating it, else a __device__ variable).
+int *status_slot(bool may_allocate);
+unsigned long long wait_limit_ns();
+void set_wait_limit_ns(unsigned long long ns);
+void debug_drop_a_loads(int launches);
+int take_debug_drop();
+// Plain host load of the mapped status word: non-zero means an earlier kernel gave up a wait;
+// reports it (return 1, message), clears it and re-zeroes the library's own split-K tickets.
+int status_check_entry();
+int status_poll(int *status_out);
 int linear_static_scratch(const LinearArgs &a, cudaStream_t stream);
 size_t static_scratch_capacity();
 void gemm_set_tile_width(int bn);
 void gemm_set_pair_mode(int mode);
 void gemm_set_trace_buffer(unsigned long long *dev_buf);
+void gemm_force_plan(int bn, int splits, int mode);
 
 // ---- pack_weights.cpp
 int pack_weight_host(const float *w, int n, int k, int layout, int8_t *packed, float *scales, int threads);
