@@ -307,8 +307,9 @@ def main():
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers of the stack (24 = the real workload)")
     ap.add_argument("--band", type=int, default=-1, help="rows per band (default: the workload's own)")
     ap.add_argument("--lanes", type=int, default=0, help="streams that bands alternate over (default 2 for cfg3)")
-    ap.add_argument("--no-fusion", action="store_true",
-                    help="run every quantizer as its own launch (ten launches per layer instead of six)")
+    ap.add_argument("--fusion", action="store_true",
+                    help="let the linears with d_model outputs emit the next linear's codes from their epilogue "
+                         "(six launches per layer instead of ten; measured slower, off by default)")
     ap.add_argument("--only-gemms", type=int, default=0, metavar="ROWS",
                     help="run the five fused linears of one layer at ROWS rows for --steps rounds with distinct "
                          "weights and exit (a small, self-ending case for ncu captures)")
@@ -366,7 +367,7 @@ def main():
     want_extras = not args.no_extras and world == 1 and args.workload == "cfg1" and args.layers == N_LAYERS
     stack, setup_s = build_stack(pkg, ref, max(rows, 2048 if want_extras else rows), band, dtype, args.layers)
     stack.set_lanes(lanes)
-    stack.set_fusion(not args.no_fusion)
+    stack.set_fusion(args.fusion)
     # every world has its own seeded tokens; weights are replicated on every rank
     per_world = rows // len(my_worlds)
     x = torch.cat([ref.make_tokens(per_world, w, dtype) for w in my_worlds]).to("cuda")

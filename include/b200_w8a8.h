@@ -203,7 +203,13 @@ int b200_w8a8_linear_requant_supported(int m, int k, int n, int q_cols);
  * (b200_w8a8_linear_static_scratch_capacity()); larger shapes are rejected with a message,
  * never truncated.  It calls no cudaMalloc / cudaFree or other allocating routine.
  * The first call on each device looks up the scratch's device address
- * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  It is also the
+ * call that fixes the footprint (the library image with its scratch is resident from then on):
+ * a warm-up call at start-up means no later call changes the free device memory.
+ * Shapes whose planner-chosen K split would overflow the scratch run with fewer, longer K
+ * ranges (down to two) before they are refused.
+ * If a kernel of the library ever gives up a bounded wait, the next entry-point call that
+ * reports it also re-zeroes the scratch's ticket counters (see b200_w8a8_poll_status).
  * All calls share the one scratch: two calls whose kernels can overlap on the GPU (different
  * streams, or different host threads on one device) race on it; calls on one stream are
  * safe, each launch leaves the counters zeroed for the next.
@@ -304,11 +310,14 @@ int b200_w8a8_stack_forward_host(void *stack, const void *x_host, void *y_host, 
  * one stream (CMakeLists.txt:46); rows of different bands never interact, so results are
  * unchanged. */
 int b200_w8a8_stack_set_lanes(void *stack, int lanes);
-/* on = 1 (default): the out, controller and down linears and the Q block of the QKV linear emit the
- * next linear's activation codes from their own epilogue (b200_w8a8_linear_requant), six launches per
- * layer; on = 0: every quantizer is its own launch, ten per layer, the reference's call structure
- * (src/world_cuda.cu:1819-2330).  Results are bit-identical either way.  The fused form needs
- * d_model % 256 == 0 and d_model <= 2048; other widths always take the ten-launch form. */
+/* on = 1: the out, controller and down linears and the Q block of the QKV linear emit the next
+ * linear's activation codes from their own epilogue (b200_w8a8_linear_requant), six launches per
+ * layer; on = 0 (default): every quantizer is its own launch, ten per layer, the reference's call
+ * structure (src/world_cuda.cu:1819-2330).  Results are bit-identical either way.  The fused form
+ * needs d_model % 256 == 0 and d_model <= 2048; other widths always take the ten-launch form.
+ * It is off by default because it measured slower on B200: a cluster of 8 CTAs fits only 15 times
+ * on the 148 SMs, and the two exchanges of row statistics add more to the epilogue than the
+ * separate quantizer launch costs. */
 int b200_w8a8_stack_set_fusion(void *stack, int on);
 /* Switches the 16-bit activation type (fp16 <-> bf16) of later forwards; both are 2 bytes,
  * so buffers are kept and only cached graphs are dropped. */

@@ -36,7 +36,7 @@ def pytest_collection_modifyitems(config, items):
     import torch
     if torch.cuda.is_available():
         return
-    skip = pytest.mark.skip(reason="no CUDA device in this container")
+    skip = pytest.mark.skip(reason="no CUDA device")
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
@@ -56,3 +56,26 @@ def pkg():
 def golden():
     import numpy as np
     return np.load(ROOT / "tests" / "golden" / "w8a8_reference_golden.npz")
+
+
+@pytest.fixture(scope="session")
+def parity_log():
+    """record(name, mismatches, positions): prints a measured mismatch count and, when the run has a
+    scratch output folder, appends it to gpurun_out/parity_counts.jsonl so the numbers quoted in the
+    design notes can be refreshed from a test run."""
+    import json
+
+    def record(name, mismatches, positions, **extra):
+        row = dict(name=name, mismatches=int(mismatches), positions=int(positions),
+                   rate=float(mismatches) / max(int(positions), 1), **extra)
+        print("PARITY", json.dumps(row))
+        out = ROOT / "gpurun_out"
+        try:
+            out.mkdir(exist_ok=True)
+            with open(out / "parity_counts.jsonl", "a") as f:
+                f.write(json.dumps(row) + "\n")
+        except OSError:
+            pass
+        return row
+
+    return record

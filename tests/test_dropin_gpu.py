@@ -43,7 +43,7 @@ def read_dump(path):
 
 
 @pytest.mark.gpu
-def test_dropin_sequence_matches_oracle(tmp_path, pkg, ref):
+def test_dropin_sequence_matches_oracle(tmp_path, pkg, ref, parity_log):
     exe = build_dropin(tmp_path, pkg)
     out = tmp_path / "dump.bin"
     r = subprocess.run([str(exe), str(out)], capture_output=True, text=True)
@@ -82,7 +82,10 @@ def test_dropin_sequence_matches_oracle(tmp_path, pkg, ref):
     assert same(i32("acc_fc1x", T, D), acc)
     q4_ref, s4_ref = ref.dequant_silu_quantize_rows(acc, s, f("sfc1x", D), f("cond", D))
     q4, s4 = i8("q4", T, D), f("sa4", T)
-    assert torch.allclose(s4, s4_ref, rtol=2e-6) and int((q4.int() - q4_ref.int()).abs().max()) <= 1
+    d4 = (q4.int() - q4_ref.int()).abs()
+    row4 = parity_log("drop-in sequence: controller codes after SiLU (q4)", int((d4 != 0).sum()), d4.numel(),
+                      max_step=int(d4.max()))
+    assert torch.allclose(s4, s4_ref, rtol=2e-6) and int(d4.max()) <= 1 and row4["mismatches"] <= 1  # measured: 0 of 24 576
     acc = ref.gemm_i8_i32(q4, i8("wfc2x", D, D))  # continue from the GPU's own codes
     assert same(i32("acc_fc2x", T, D), acc)
     after_ctrl = ref.dequant_add_residual(acc, s4, f("sfc2x", D), after_attn)
@@ -94,7 +97,10 @@ def test_dropin_sequence_matches_oracle(tmp_path, pkg, ref):
     assert same(i32("acc_fc1", T, HID), acc)
     q6_ref, s6_ref = ref.dequant_silu_quantize_rows(acc, s, f("sfc1", HID), None)
     q6, s6 = i8("q6", T, HID), f("sa6", T)
-    assert torch.allclose(s6, s6_ref, rtol=2e-6) and int((q6.int() - q6_ref.int()).abs().max()) <= 1
+    d6 = (q6.int() - q6_ref.int()).abs()
+    row6 = parity_log("drop-in sequence: MLP codes after SiLU (q6)", int((d6 != 0).sum()), d6.numel(),
+                      max_step=int(d6.max()))
+    assert torch.allclose(s6, s6_ref, rtol=2e-6) and int(d6.max()) <= 1 and row6["mismatches"] <= 1  # measured: 0 of 49 152
     acc = ref.gemm_i8_i32(q6, i8("wfc2", D, HID))
     assert same(i32("acc_fc2", T, D), acc)
     assert same(f("next", T, D), ref.dequant_gated_residual(acc, s6, f("sfc2", D), after_ctrl, f("g1", D)))

@@ -152,21 +152,22 @@ def test_fused_linear_strided_output(pkg, ref):
 
 
 @pytest.mark.parametrize("m,k,n", [(16, 2048, 2048), (64, 8192, 2048), (128, 2048, 8192), (32, 2048, 2048),
-                                   (100, 1024, 520), (512, 8192, 2048)])
-@pytest.mark.parametrize("forced", [0, (64 | (4 << 16)), (128 | (2 << 16)), (256 | (8 << 16))])
+                                   (100, 1024, 520), (512, 8192, 2048), (48, 9 * 128, 256)])
+@pytest.mark.parametrize("forced", [(0, 0), (64, 4), (128, 2), (256, 8)])
 def test_split_k_linear_bit_exact(pkg, ref, m, k, n, forced):
     """Skinny / few-tile shapes with the K range split over several CTAs: integer partial sums are
     added in the workspace, so the result is identical to the unsplit kernel and to the oracle.
-    `forced` pins tile width and split count; 0 lets the planner choose."""
+    `forced` pins (tile width, K ranges); (0, 0) lets the planner choose.  (9 K slabs in 4 ranges would
+    leave the last range empty: the launcher must lower the count rather than reduce a stale accumulator.)"""
     g = torch.Generator().manual_seed(m + k)
     a, b = codes(m, k, 11), codes(n, k, 12)
     sx = torch.rand(m, generator=g) * 0.05 + 0.01
     sw = torch.rand(n, generator=g) * 2e-4 + 1e-5
     res = torch.randn(m, n, generator=g).half()
     want = ref.linear_w8a8(a, sx, b, sw, residual=res, out_dtype=torch.float16)
-    splits = forced >> 16 if forced else 8
+    splits = forced[1] if forced[1] else 8
     ws = torch.zeros(4096 + splits * m * n * 4, dtype=torch.uint8, device=DEV)
-    pkg.lib().b200_w8a8_set_tile_width(forced)
+    pkg.lib().b200_w8a8_debug_force_plan(forced[0], forced[1], 1 if forced[1] else 0)
     try:
         for _ in range(2):  # twice through the same workspace: it must come back zero-filled where it matters
             got = pkg.linear(a.to(DEV), sx.to(DEV), b.to(DEV), sw.to(DEV), residual=res.to(DEV),
@@ -175,7 +176,7 @@ def test_split_k_linear_bit_exact(pkg, ref, m, k, n, forced):
             assert torch.equal(got.cpu(), want)
             assert int(ws[:4096].view(torch.int32).abs().max()) == 0  # ticket counters are back at zero
     finally:
-        pkg.lib().b200_w8a8_set_tile_width(0)
+        pkg.lib().b200_w8a8_debug_force_plan(0, 0, 0)
 
 
 def test_split_k_planner_reports_workspace(pkg):
@@ -200,7 +201,7 @@ def test_cluster_split_k_linear_bit_exact(pkg, ref, m, k, n, bn, splits, out_dty
     bias = torch.randn(n, generator=g) * 0.1
     res = torch.randn(m, n, generator=g).to(out_dtype)
     want = ref.linear_w8a8(a, sx, b, sw, bias=bias, residual=res, out_dtype=out_dtype)
-    pkg.lib().b200_w8a8_set_tile_width(bn | (splits << 16) | (2 << 24))
+    pkg.lib().b200_w8a8_debug_force_plan(bn, splits, 2)
     try:
         got = pkg.linear(a.to(DEV), sx.to(DEV), b.to(DEV), sw.to(DEV), bias=bias.to(DEV), residual=res.to(DEV),
                          out_dtype=out_dtype)
@@ -209,7 +210,7 @@ def test_cluster_split_k_linear_bit_exact(pkg, ref, m, k, n, bn, splits, out_dty
         acc = pkg.gemm_i8_i32(a.to(DEV), b.to(DEV))
         assert torch.equal(acc.cpu(), ref.gemm_i8_i32(a, b))
     finally:
-        pkg.lib().b200_w8a8_set_tile_width(0)
+        pkg.lib().b200_w8a8_debug_force_plan(0, 0, 0)
 
 
 @pytest.fixture

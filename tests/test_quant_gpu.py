@@ -84,7 +84,7 @@ def test_rms_norm_quantize_rows_bit_exact(pkg, ref, dtype, rows, cols, variant):
 
 @pytest.mark.parametrize("act", [1, 2])
 @pytest.mark.parametrize("rows,cols,with_bias", [(128, 2048, True), (512, 8192, False), (19, 72, True)])
-def test_dequant_act_quantize_rows(pkg, ref, act, rows, cols, with_bias):
+def test_dequant_act_quantize_rows(pkg, ref, parity_log, act, rows, cols, with_bias):
     g = torch.Generator().manual_seed(rows + act)
     acc = torch.randint(-120000, 120000, (rows, cols), generator=g, dtype=torch.int32)
     sa = torch.rand(rows, generator=g) * 0.05 + 0.01
@@ -98,9 +98,13 @@ def test_dequant_act_quantize_rows(pkg, ref, act, rows, cols, with_bias):
     assert s.data_ptr() == sa_dev.data_ptr()
     assert torch.allclose(s.cpu(), s_ref, rtol=2e-6, atol=0)
     diff = (q.cpu().int() - q_ref.int()).abs()
+    row = parity_log(f"dequant_act_quantize_rows act={act} {rows}x{cols}", int((diff != 0).sum()), diff.numel(),
+                     max_step=int(diff.max()))
     assert int(diff.max()) <= 1
-    # exp/tanh differ in the last ulps between libraries: a code may move across a rounding tie
-    assert float((diff != 0).float().mean()) < 2e-3
+    # exp/tanh differ in the last ulps between libraries: a code may move across a rounding tie.
+    # Measured on B200: 8 and 6 of 4 194 304 positions (1.9e-6, 1.4e-6) at 512 x 8192, none at the small
+    # sizes; the bound is twice the largest measured rate (one position at 128 x 2048).
+    assert row["rate"] < 4e-6
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])

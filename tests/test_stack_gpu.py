@@ -107,7 +107,7 @@ def test_stack_driver_equals_operator_composition(pkg, ref, dtype, rows, band, s
     stack.close()
 
 
-def test_stack_end_to_end_against_cpu_oracle(pkg, ref):
+def test_stack_end_to_end_against_cpu_oracle(pkg, ref, parity_log):
     n_layers, rows = 2, 160
     stack = pkg.LinearStack(D, NQKV, HID, n_layers, max_rows=rows)
     layers = []
@@ -119,8 +119,11 @@ def test_stack_end_to_end_against_cpu_oracle(pkg, ref):
     want = ref.stack_forward(x, layers, steps=1)
     got = stack.forward(x.to(DEV)).cpu()
     ulp = ref.ulp_distance_f16(got, want)
-    # a GELU ulp can move a re-quantized code across a tie; downstream that is a few 16-bit ulps
-    assert float((ulp > 2).float().mean()) < 0.02
+    row = parity_log("stack output (2 layers, d=256) beyond 2 fp16 ulp of the pure-CPU oracle", int((ulp > 2).sum()),
+                     ulp.numel(), max_ulp=int(ulp.max()), differing=int((ulp > 0).sum()))
+    # a GELU ulp can move a re-quantized code across a tie; downstream that is a few 16-bit ulps.
+    # Measured on B200: no element beyond 2 ulp, largest distance 1 ulp, 2 of 40 960 elements differ at all.
+    assert row["mismatches"] == 0 and row["max_ulp"] <= 2 and row["differing"] <= 4
     assert float((got.float() - want.float()).abs().max()) <= 0.02 * float(want.float().abs().max())
     stack.close()
 

@@ -19,7 +19,7 @@ def codes(rows, cols, seed):
 
 @pytest.mark.parametrize("m,k,n,dtype", [(16, 2048, 2048, torch.float16), (128, 8192, 2048, torch.bfloat16),
                                          (100, 1024, 520, torch.float32)])
-def test_static_scratch_linear_matches_the_allocating_entry_point_twice_in_a_row(pkg, m, k, n, dtype):
+def test_static_scratch_linear_matches_the_allocating_entry_point_twice_in_a_row(pkg, ref, m, k, n, dtype):
     g = torch.Generator().manual_seed(m + n)
     a, b = codes(m, k, 21).to(DEV), codes(n, k, 22).to(DEV)
     sx = (torch.rand(m, generator=g) * 0.05 + 0.01).to(DEV)
@@ -30,12 +30,20 @@ def test_static_scratch_linear_matches_the_allocating_entry_point_twice_in_a_row
     out1 = torch.empty(m, n, dtype=dtype, device=DEV)
     out2 = torch.empty(m, n, dtype=dtype, device=DEV)
     pkg.linear_static_scratch(a, sx, b, sw, bias=bias, residual=res, out=out1)
+    torch.cuda.synchronize()
+    # the first call fixes the footprint (module image, scratch address look-up); from then on a call
+    # must leave the device's free memory exactly as it found it
+    free_before = torch.cuda.mem_get_info()[0]
     pkg.linear_static_scratch(a, sx, b, sw, bias=bias, residual=res, out=out2)  # same scratch, second call
     torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "the no-allocation entry point changed the free device memory"
     assert pkg.poll_status() == 0
     # both paths add the same integers and run the same fp32 epilogue: identical bits, no tolerance
     assert torch.equal(out1.view(torch.uint8), want.view(torch.uint8))
     assert torch.equal(out2.view(torch.uint8), want.view(torch.uint8))
+    # and the CPU oracle agrees (no activation in this epilogue: exact)
+    want_cpu = ref.linear_w8a8(a.cpu(), sx.cpu(), b.cpu(), sw.cpu(), bias=bias.cpu(), residual=res.cpu(), out_dtype=dtype)
+    assert torch.equal(out1.cpu().view(torch.uint8), want_cpu.view(torch.uint8))
 
 
 def test_static_scratch_linear_rejects_what_does_not_fit(pkg):

@@ -38,6 +38,10 @@ NVCC_FLAGS = [
 ]
 
 
+if os.environ.get("B200_TRACE"):  # tuning builds only: per-CTA timestamps inside the GEMM kernels
+    NVCC_FLAGS.append("-DB200_TRACE")
+
+
 def nvcc() -> str:
     for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", "nvcc"):
         if cand and (os.path.isfile(cand) or cand == "nvcc"):

@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     pdl_trigger();
     if (threadIdx.x == 0) {
+        trace_mark(p, 0);
         for (int s = 0; s < kRqStages; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_empty[s], 1);
@@ -208,6 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     cluster_sync_all();  // every CTA's barriers exist before any CTA signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) trace_mark(p, 1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -272,6 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
+                    if (t == 0 && kb == 0) trace_mark(p, 2);
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * kRqStageBytes);
                     const uint64_t da = umma_smem_desc_k128(sa);
@@ -283,6 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (++s == kRqStages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit(&bar_tfull[b]);
+                if (t == 0) trace_mark(p, 3);
                 ++t;
             }
         }
@@ -324,6 +328,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             ok = __all_sync(0xffffffffu, ok && carry_ok);
             ok = pair_vote(vote_bar, ok);  // the two warps of a sub-partition go on together or not at all
             if (!ok) break;
+            const bool tr = warp == 2 && lane == 0 && t == 0;
+            if (tr) trace_mark(p, 4);
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(b * RQ_BN + half * (RQ_BN / 2));
             const bool quant = grp == 0;
@@ -378,6 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 continue;
             }
             tmem_st_wait();
+            if (tr) trace_mark(p, 5);
             const uint32_t xph = qi & 1u;
             bool okx = true;
             float inv = 1.0f;
@@ -396,6 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 okx = mbar_wait_bounded_cluster(&bar_x[0], xph, wctx, KS_TIMEOUT_ROW_EXCHANGE);
                 okx = __all_sync(0xffffffffu, okx);
+                if (tr) trace_mark(p, 6);
                 double tot = 0.0;
                 for (int s = 0; s < cs; ++s) tot += ss_x[s * BM + trow];  // fixed order: identical in every CTA
                 inv = (float)(1.0 / sqrt(tot / (double)rp.q_cols + (double)rp.eps));
@@ -415,6 +423,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             // ---- exchange 2: row maxima.  Without the first exchange in between, a fast CTA could write
             // the next unit's maxima while a slow one still reads this unit's: two buffers alternate then.
+            if (tr) trace_mark(p, 7);
             float *mx_buf = (rms || xph == 0) ? mx_x : reinterpret_cast<float *>(ss_x);
             if (half == 1) mx_half[trow] = amax;
             okx = pair_vote(vote_bar, okx);
@@ -431,6 +440,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 okx = mbar_wait_bounded_cluster(&bar_x[1], xph, wctx, KS_TIMEOUT_ROW_EXCHANGE);
                 okx = __all_sync(0xffffffffu, okx);
             }
+            if (tr) trace_mark(p, 8);
             if (okx) {
                 float m = 0.0f;
                 for (int s = 0; s < cs; ++s) m = fmaxf(m, mx_buf[s * BM + trow]);
@@ -459,6 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                 }
             }
+            if (tr) trace_mark(p, 9);
             carry_ok = okx;
             ++qi;
             tc_fence_before_sync();
@@ -479,6 +490,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         __syncthreads();
     }
+    if (threadIdx.x == 0) trace_mark(p, 10);
     tc_fence_before_sync();
     cluster_sync_all();  // no CTA exits while another may still write its shared memory or signal its barriers
     if (warp == 1) {
@@ -595,6 +607,7 @@ int linear_requant(const LinearArgs &a_in, const RowQuantSpec &qs, cudaStream_t 
     p.vec_ok = 1;
     p.tma_store = 1;
     p.static_weights = a.static_weights;
+    p.trace = gemm_trace_buffer();
     p.status = status_slot(true);
     p.wait_limit_ns = wait_limit_ns();
     p.debug_drop_a_load = take_debug_drop();

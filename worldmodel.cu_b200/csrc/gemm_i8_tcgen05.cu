@@ -1089,6 +1089,7 @@ void gemm_force_plan(int bn, int splits, int mode) {
 }
 void gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 void gemm_set_trace_buffer(unsigned long long *dev_buf) { g_trace = dev_buf; }
+unsigned long long *gemm_trace_buffer() { return g_trace; }
 
 int gemm_can_implement(const LinearArgs &a, bool verbose) {
     auto no = [&](const char *why) {

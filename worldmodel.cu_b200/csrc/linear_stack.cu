@@ -55,7 +55,8 @@ struct Stack {
         float *h = nullptr;          // [band, hidden] fp32 hidden before re-quantization
     } scratch[2];
     int lanes = 1;
-    int fusion = 1;      // linears with d_model output columns emit the next linear's codes from their epilogue
+    int fusion = 0;      // 1: linears with d_model output columns emit the next linear's codes from their epilogue
+                         // (off by default: measured slower on B200 at every row count, see stack_set_fusion)
     bool fuse_ok = false;  // the shapes allow it (d_model a multiple of 256, at most 2048)
     cudaStream_t lane_stream = nullptr;   // stream of the second lane
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
@@ -266,6 +267,7 @@ void *b200_w8a8_stack_create(int d_model, int n_qkv, int d_hidden, int n_layers,
              d_hidden, n_layers, max_rows, act_dtype);
         return nullptr;
     }
+    status_slot(true);  // the status word exists before the first (possibly captured) forward
     Stack *s = new Stack();
     s->d = d_model; s->n_qkv = n_qkv; s->hidden = d_hidden; s->n_layers = n_layers; s->max_rows = max_rows;
     s->band_rows = band_rows > 0 && band_rows < max_rows ? band_rows : max_rows;

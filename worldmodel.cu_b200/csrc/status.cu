@@ -42,6 +42,10 @@ int *status_slot(bool may_allocate) {
     if (!g_mapped_dev && may_allocate && !g_map_tried) {
         g_map_tried = true;
         void *h = nullptr, *d = nullptr;
+        // the first launch of a process may sit inside a stream capture, where allocating calls are
+        // refused unless the thread's capture mode is relaxed for their duration
+        cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+        cudaThreadExchangeStreamCaptureMode(&mode);
         if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
             *reinterpret_cast<volatile int *>(h) = 0;
             if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess && d) {
@@ -51,6 +55,7 @@ int *status_slot(bool may_allocate) {
                 cudaFreeHost(h);
             }
         }
+        cudaThreadExchangeStreamCaptureMode(&mode);
         cudaGetLastError();  // a refused mapping is not an error of the caller's launch
     }
     if (g_mapped_dev) return g_mapped_dev;

@@ -171,6 +171,7 @@ size_t static_scratch_capacity();
 void gemm_set_tile_width(int bn);
 void gemm_set_pair_mode(int mode);
 void gemm_set_trace_buffer(unsigned long long *dev_buf);
+unsigned long long *gemm_trace_buffer();
 void gemm_force_plan(int bn, int splits, int mode);
 
 // ---- pack_weights.cpp
