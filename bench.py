@@ -1,18 +1,21 @@
 """Benchmark of the W8A8 linear stack (the hot path) on B200.
 
     python bench.py --gpus N --steps K --warmup W            # this library, one JSON line
-    python bench.py --impl reference --gpus N --steps K ...  # the CPU reference arm
+    python bench.py --impl reference --gpus N --steps K ...  # the reference arm
 
-A step is one denoising pass of the 24-layer linear stack over one batch of synthetic
-tokens (the workload of the headline config: M=512 rows, d_model 2048, QKV 6144, MLP 8192,
-fp16 activations).  `value` is int8 tera-operations per second over all GPUs with the
-tokens already resident in HBM; `e2e` is the same metric through the host-buffer entry
-point with the H2D / D2H copies inside the timed region.  With N > 1 every rank runs its
-own independent world of the same size (rows shard across GPUs, no collective): weak
-scaling, time = max over ranks.
+A step is one denoising pass of the 24-layer linear stack over the sharded config: 64
+independent worlds x 2048 token rows (131 072 rows, d_model 2048, QKV 6144, MLP 8192, fp16
+activations), the worlds dealt out over the N ranks with replicated weights and no collective on
+the data path: strong scaling, time = max over ranks.  `value` is int8 tera-operations per
+second over all GPUs with the tokens already resident in HBM, the median of `--repeats` timed
+passes of K steps; `e2e` is the same metric through the host-buffer entry point with the H2D /
+D2H copies inside the timed region.  At N = 1 `extras` adds the other configs (M=512 one pass,
+M=2048 four chained passes in bf16, the skinny weight-bound linears, the QKV consumer epilogue).
 
-The CPU oracle under oracle/ is used here only by the `cpu_baseline` leg and by
-`--impl reference`; nothing measured as the product touches it.
+`--impl reference` times the reference's own CUDA operators (its src/world_cuda_ops.cu compiled
+where it lies into oracle/_ref/) in the reference's per-layer call order on the same rows, or,
+when that library was not built, the CPU oracle port.  The CPU oracle under oracle/ is used only
+by the `cpu_baseline` leg and by that arm; nothing measured as the product touches it.
 """
 from __future__ import annotations
 
@@ -33,7 +36,8 @@ LINEARS = [("qkv", N_QKV, D_MODEL), ("out", D_MODEL, D_MODEL), ("ctrl", D_MODEL,
            ("up", D_HIDDEN, D_MODEL), ("down", D_MODEL, D_HIDDEN)]
 OPS_PER_ROW_LAYER = 2 * sum(n * k for _, n, k in LINEARS)  # 109,051,904
 WEIGHT_BYTES_LAYER = sum(n * k for _, n, k in LINEARS)     # 54,525,952
-NCU_DRAM_BYTES_PER_LAYER_M512 = 69.5e6
+# DRAM read+write of the five GEMM launches of one layer from the committed ncu captures (profiles/)
+NCU_DRAM_BYTES_PER_LAYER = {512: 69.5e6}
 WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),
@@ -41,6 +45,29 @@ WORKLOADS = {
     "cfg3": (None, 1, "fp16", 8192),    # 64 worlds x 2048 rows dealt over the ranks (strong scaling)
 }
 CFG3_WORLDS, CFG3_ROWS_PER_WORLD = 64, 2048
+
+
+def layer_gemm_algorithmic_bytes(m: int, e: int = 2) -> int:
+    """Bytes the five fused linears of one layer must move at M rows: A8 codes and W8 codes in, both scale
+    vectors, the residual where there is one, and the result (e bytes per element; the up linear's hidden
+    is fp32)."""
+    total = 0
+    for name, n, k in LINEARS:
+        total += m * k + n * k + 4 * m + 4 * n
+        total += (4 if name == "up" else e) * m * n
+        if name in ("out", "ctrl", "down"):
+            total += e * m * n
+    return total
+
+
+def workload_string(name: str, layers: int, worlds: int = CFG3_WORLDS) -> str:
+    """The same text from both arms of the bench, so that their lines can be matched."""
+    if name == "cfg3":
+        return (f"cfg3: {layers}-layer W8A8 linear stack, {worlds} independent worlds x {CFG3_ROWS_PER_WORLD} rows = "
+                f"{worlds * CFG3_ROWS_PER_WORLD} token rows dealt over the GPUs, d=2048, qkv 6144, mlp 8192, fp16")
+    rows, chained, dt_name, _ = WORKLOADS[name]
+    return (f"{name}: {layers}-layer W8A8 linear stack, M={rows} rows per GPU, {chained} chained pass(es) per step, "
+            f"d=2048, qkv 6144, mlp 8192, {dt_name}")
 SKINNY_SHAPES = [(2048, 2048), (2048, 8192), (8192, 2048)]  # (K, N) of config 4
 
 
@@ -140,7 +167,7 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
-# reference arm / CPU baseline: the oracle port on the host cores
+# CPU baseline: the oracle port on the host cores
 # ------------------------------------------------------------------------------------------
 def cpu_layer_seconds(ref, rows: int, layer_weights, x):
     """One layer of the stack through the oracle with the reference's own int32 matmul expression."""
@@ -157,10 +184,6 @@ def cpu_layer_seconds(ref, rows: int, layer_weights, x):
     return dt
 
 
-def small_layer_for_cpu(ref):
-    return ref.make_layer(0)
-
-
 def use_all_host_threads():
     """torchrun pins OMP_NUM_THREADS=1; the CPU arm should use every core the box offers."""
     import torch
@@ -174,11 +197,11 @@ def use_all_host_threads():
 
 
 def run_cpu_baseline(budget_s: float = 15.0):
-    """Times a bounded sample of the headline workload on the host: rows of one layer."""
+    """Times a bounded sample of the workload on the host: rows of one layer of one world."""
     import torch
     ref = load_oracle()
     cores = use_all_host_threads()
-    lw = small_layer_for_cpu(ref)
+    lw = ref.make_layer(0)
     x = ref.make_tokens(512, 0, torch.float16)
     t_probe = cpu_layer_seconds(ref, 32, lw, x)
     rows = int(max(32, min(512, 32 * budget_s / max(t_probe, 1e-3))))
@@ -186,8 +209,93 @@ def run_cpu_baseline(budget_s: float = 15.0):
     dt = cpu_layer_seconds(ref, rows, lw, x)
     tops = rows * OPS_PER_ROW_LAYER / dt / 1e12
     return {"value": tops, "unit": "TOP/s", "cores": cores, "kind": "port",
-            "sample": f"1 of 24 layers of the stack on {rows} of 512 rows, oracle port with the reference's "
+            "sample": f"1 of 24 layers of the stack on {rows} rows of world 0, oracle port with the reference's "
                       f"int32 matmul expression, {dt:.2f} s"}
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the reference's own CUDA operators in its per-layer call order
+# ------------------------------------------------------------------------------------------
+class ReferenceCudaStack:
+    """The reference's W8A8 operator sequence for the linears of a layer (src/world_cuda.cu:1819-2330 with
+    attention left out, as in the stack): norm->A8, int8 GEMM into the int32 scratch, consumer / dequant
+    kernels, on fp32 tokens, 24 distinct weight sets.  Launched one by one on the default stream, as the
+    reference does (its operators take no stream)."""
+
+    def __init__(self, rows, n_heads=32, d_head=64):
+        import torch
+        sys.path.insert(0, str(ROOT / "oracle"))
+        import ref_cuda_ops as rk
+        self.rk, self.rows = rk, rows
+        dev = "cuda"
+        d, nq, hid = D_MODEL, N_QKV, D_HIDDEN
+        g = torch.Generator().manual_seed(11)
+        rnd8 = lambda *shape: torch.randint(-127, 128, shape, dtype=torch.int8, device=dev)
+        self.ws = {name: [rnd8(n, k) for _ in range(N_LAYERS)] for name, n, k in LINEARS}
+        self.sw = {name: torch.rand(n, device=dev) * 1e-3 for name, n, k in LINEARS}
+        self.x = torch.randn(rows, d, device=dev)
+        self.x1, self.x2, self.x3 = (torch.empty_like(self.x) for _ in range(3))
+        self.gamma = torch.randn(d, device=dev) * 0.05
+        self.gate = torch.ones(d, device=dev)
+        self.a8 = rnd8(rows, hid)
+        self.sa = torch.rand(rows, device=dev) * 1e-2
+        self.acc = torch.empty(rows, hid, dtype=torch.int32, device=dev)
+        self.n_heads, self.d_head = n_heads, d_head
+        self.n_kv = (nq // d_head - n_heads) // 2
+        self.q = torch.empty(n_heads, rows, d_head, device=dev)
+        self.k = torch.empty(self.n_kv, rows, d_head, device=dev)
+        self.v = torch.empty(self.n_kv, rows, d_head, device=dev)
+        self.pos = [torch.randint(0, hi, (rows,), generator=g).to(dev) for hi in (32, 16, 64)]
+        self.xy = (torch.rand(d_head // 8, generator=g) * 6).to(dev)
+        self.inv_t = torch.rand(d_head // 2 - 2 * (d_head // 8), generator=g).to(dev)
+
+    def gemm(self, name, layer):
+        n, k = next((n, k) for nm, n, k in LINEARS if nm == name)
+        self.rk.call("gemm_i8_i32", self.a8, self.ws[name][layer], self.acc, self.rows, k, n)
+
+    def layers(self, n_layers=N_LAYERS):
+        rk, rows, d, nq, hid = self.rk, self.rows, D_MODEL, N_QKV, D_HIDDEN
+        x, x1, x2, x3, a8, sa, acc, sw = self.x, self.x1, self.x2, self.x3, self.a8, self.sa, self.acc, self.sw
+        for l in range(n_layers):
+            rk.call("rms_norm_quantize_rows_i8", x, self.gamma, None, a8, sa, rows, d, 1e-6)
+            self.gemm("qkv", l)
+            rk.call("qkv_fused_rms_rope_i32_dequant", acc, sa, sw["qkv"], self.q, self.k, self.v, *self.pos, self.xy,
+                    self.inv_t, rows, self.n_heads, self.n_kv, self.d_head, 32, 16, 1e-6)
+            rk.call("quantize_rows_f32_i8", self.q, a8, sa, rows, d)  # stands in for the attention output [rows, d]
+            self.gemm("out", l)
+            rk.call("dequant_gated_residual_f32", acc, sa, sw["out"], x, self.gate, x1, rows, d)
+            rk.call("rms_norm_quantize_rows_i8", x1, self.gamma, None, a8, sa, rows, d, 1e-6)
+            self.gemm("ctrl", l)
+            rk.call("dequant_add_residual_f32", acc, sa, sw["ctrl"], x1, x2, rows, d)
+            rk.call("rms_norm_quantize_rows_i8", x2, self.gamma, None, a8, sa, rows, d, 1e-6)
+            self.gemm("up", l)
+            rk.call("dequant_silu_quantize_rows_i8", acc, sa, sw["up"], None, a8, sa, rows, hid)
+            self.gemm("down", l)
+            rk.call("dequant_gated_residual_f32", acc, sa, sw["down"], x2, self.gate, x3, rows, d)
+
+
+def reference_cuda_available():
+    import torch
+    if not torch.cuda.is_available():
+        return "no CUDA device"
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import ref_cuda_ops as rk
+    if not rk.available():
+        return ("oracle/_ref/libworld_cuda_ops_ref.so is not built (needs the reference checkout and a CUTLASS "
+                "header tree at build time)")
+    return None
+
+
+def event_ms(fn, reps):
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
 
 
 def run_reference_arm(args):
@@ -195,14 +303,50 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    rows_w, chained, dt_name, _ = WORKLOADS[args.workload]
+    total_rows = args.worlds * CFG3_ROWS_PER_WORLD if args.workload == "cfg3" else rows_w
+    line = {"impl": "reference", "metric": "w8a8_linear_stack_int8_tops", "unit": "TOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+            "scaling": "strong" if args.workload == "cfg3" else "weak", "vs_baseline": None, "dtype": "s8",
+            "data": "synthetic", "config": {"workload": workload_string(args.workload, args.layers, args.worlds)}}
+    why_not = reference_cuda_available()
+    if why_not is None:
+        # The reference has no multi-GPU mode and no CPU implementation of this path: one process runs its
+        # CUDA operators over the whole job on one GPU, in slices of 16 384 rows (its int32 scratch is
+        # 4 * rows * 8192 bytes), every slice through all layers, `chained` times.
+        torch.cuda.set_device(0)
+        slice_rows = min(total_rows, 16384)
+        n_slices = -(-total_rows // slice_rows)
+        stack = ReferenceCudaStack(slice_rows)
+
+        def step():
+            for _ in range(n_slices * chained):
+                stack.layers(args.layers)
+        for _ in range(args.warmup):
+            step()
+        ms = event_ms(step, args.steps)
+        ops = n_slices * slice_rows * OPS_PER_ROW_LAYER * args.layers * chained
+        tops = ops / (ms * 1e-3) / 1e12
+        sample = (f"the reference's own CUDA operators (src/world_cuda_ops.cu built with its --use_fast_math, CUTLASS "
+                  f"Sm80 mma.sync GEMM) on ONE GPU: the whole job, {n_slices} slice(s) of {slice_rows} rows x "
+                  f"{args.layers} layers x {chained} pass(es) per step, 14 eager launches per layer, fp32 tokens")
+        line.update(value=tops, ms_per_step=ms, gpu_launches=int(14 * args.layers * n_slices * chained * args.steps),
+                    cpu_baseline={"value": tops, "unit": "TOP/s", "cores": 1, "kind": "reference", "sample": sample},
+                    e2e={"value": tops, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        try:
+            line["cpu_port"] = run_cpu_baseline(10.0)
+        except Exception as exc:
+            line["cpu_port"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+        print(json.dumps(line))
+        return 0
+    # no reference CUDA library on this box: the CPU oracle port on the host cores, a bounded sample per step
     ref = load_oracle()
     cores = use_all_host_threads()
-    lw = small_layer_for_cpu(ref)
+    lw = ref.make_layer(0)
     x = ref.make_tokens(512, 0, torch.float16)
     t_probe = cpu_layer_seconds(ref, 32, lw, x)
     total = max(args.steps + args.warmup, 1)
-    per_step_budget = 150.0 / total
-    rows = int(max(32, min(512, 32 * per_step_budget / max(t_probe, 1e-3))))
+    rows = int(max(32, min(512, 32 * (150.0 / total) / max(t_probe, 1e-3))))
     rows -= rows % 32
     for _ in range(args.warmup):
         cpu_layer_seconds(ref, rows, lw, x)
@@ -211,20 +355,11 @@ def run_reference_arm(args):
         cpu_layer_seconds(ref, rows, lw, x)
     dt = time.perf_counter() - t0
     tops = args.steps * rows * OPS_PER_ROW_LAYER / dt / 1e12
-    sample = (f"each step = 1 of 24 layers on {rows} of 512 rows (bounded sample of the cfg1 stack), oracle port "
-              f"with the reference's int32 matmul expression on {cores} host threads")
-    line = {"impl": "reference", "metric": "w8a8_linear_stack_int8_tops", "value": tops, "unit": "TOP/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
-            "config": {"workload": "cfg1: 24-layer W8A8 linear stack, M=512, d=2048, qkv 6144, mlp 8192, fp16"},
-            "cpu_baseline": {"value": tops, "unit": "TOP/s", "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": tops, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    # Beside the CPU figure: the reference's own CUDA operators on this box's GPU, when they were built.
-    try:
-        line["reference_cuda_ops_same_gpu"] = (run_reference_cuda_ops() if torch.cuda.is_available()
-                                               else {"unavailable": "no CUDA device"})
-    except Exception as exc:  # a comparator must never cost the line
-        line["reference_cuda_ops_same_gpu"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    sample = (f"each step = 1 of {args.layers} layers on {rows} rows of world 0 (bounded sample of the workload), oracle "
+              f"port with the reference's int32 matmul expression on {cores} host threads")
+    line.update(value=tops, ms_per_step=dt / args.steps * 1e3, reference_cuda_unavailable=why_not,
+                cpu_baseline={"value": tops, "unit": "TOP/s", "cores": cores, "kind": "port", "sample": sample},
+                e2e={"value": tops, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
     print(json.dumps(line))
     return 0
 
@@ -233,7 +368,6 @@ def run_reference_arm(args):
 # this library
 # ------------------------------------------------------------------------------------------
 def build_stack(pkg, ref, rows, band_rows, dtype, n_layers=N_LAYERS):
-    import torch
     t0 = time.perf_counter()
     stack = pkg.LinearStack(D_MODEL, N_QKV, D_HIDDEN, n_layers, max_rows=rows, band_rows=band_rows, dtype=dtype)
     for l in range(n_layers):
@@ -279,7 +413,8 @@ def time_gemm_kernels(pkg, rows, stream, iters=3):
 
         def run():
             for w in ws:
-                pkg.linear(a8, sx, w, sw, n=n, w_layout=pkg.W_SLAB128, residual=residual, act=act, out=out)
+                pkg.linear(a8, sx, w, sw, n=n, w_layout=pkg.W_SLAB128, residual=residual, act=act, out=out,
+                           const_weights=True)
         # replayed as a graph so that the device, not the Python launch rate, sets the pace
         with torch.cuda.stream(stream):
             run()
@@ -297,10 +432,14 @@ def time_gemm_kernels(pkg, rows, stream, iters=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=5, help="timed passes of --steps steps; the median is reported")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--worlds", type=int, default=CFG3_WORLDS,
+                    help="cfg3 only: worlds of 2048 rows in the job (64 = the real workload; fewer for a small, "
+                         "self-ending profiler capture)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configs reported under `extras`")
@@ -310,20 +449,9 @@ def main():
     ap.add_argument("--fusion", action="store_true",
                     help="let the linears with d_model outputs emit the next linear's codes from their epilogue "
                          "(six launches per layer instead of ten; measured slower, off by default)")
-    ap.add_argument("--only-gemms", type=int, default=0, metavar="ROWS",
-                    help="run the five fused linears of one layer at ROWS rows for --steps rounds with distinct "
-                         "weights and exit (a small, self-ending case for ncu captures)")
-    ap.add_argument("--only-qkv-heads", type=int, default=0, metavar="TOKENS",
-                    help="run the QKV linear with the RMSNorm + RoPE epilogue (heads 32/16 x 64) at TOKENS rows for "
-                         "--steps rounds with distinct weights and exit (a small case for ncu captures)")
-    ap.add_argument("--only-quant", type=int, default=0, metavar="ROWS",
-                    help="run the three quantizers of a layer (RMSNorm->A8 of fp16 rows, A8 of the first 2048 of 6144 "
-                         "fp16 columns, A8 of 8192 fp32 columns) at ROWS rows for --steps rounds and exit")
-    ap.add_argument("--only-grouped", type=int, default=0, metavar="ROWS",
-                    help="run one grouped call of 24 skinny linears (ROWS rows each, K=2048, N=8192, distinct weights) "
-                         "for --steps rounds and exit (a small case for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
 
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -341,30 +469,31 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
 
+    def max_over_ranks(v):
+        if world == 1:
+            return float(v)
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     pkg, ref = load_package(), load_oracle()
     pkg.lib()  # raises if the CUDA library is missing
-    if args.only_gemms:
-        return run_only_gemms(pkg, args.only_gemms, max(args.steps, 1))
-    if args.only_qkv_heads:
-        return run_only_qkv_heads(pkg, args.only_qkv_heads, max(args.steps, 1))
-    if args.only_grouped:
-        return run_only_grouped(pkg, args.only_grouped, max(args.steps, 1))
-    if args.only_quant:
-        return run_only_quant(pkg, args.only_quant, max(args.steps, 1))
     peaks = measured_peaks()
     rows, chained, dt_name, band = WORKLOADS[args.workload]
     sharding = _load("w8a8_sharding", ROOT / "worldmodel.cu_b200" / "sharding.py")
-    my_worlds = [rank]  # weak scaling: one independent world per rank, seeded by its global id
+    my_worlds = [rank]  # cfg1 / cfg2: one independent world per rank, seeded by its global id (weak scaling)
     if args.workload == "cfg3":
-        my_worlds = sharding.world_seeds(CFG3_WORLDS, world, rank)
+        my_worlds = sharding.world_seeds(args.worlds, world, rank)
         rows = len(my_worlds) * CFG3_ROWS_PER_WORLD
+    if rows == 0:
+        raise SystemExit(f"rank {rank} of {world} has no world to run: use at most {args.worlds} GPUs")
     dtype = torch.float16 if dt_name == "fp16" else torch.bfloat16
     use_graph = not args.no_graph
     if args.band >= 0:
         band = args.band
     lanes = args.lanes if args.lanes > 0 else (2 if args.workload == "cfg3" else 1)
 
-    want_extras = not args.no_extras and world == 1 and args.workload == "cfg1" and args.layers == N_LAYERS
+    want_extras = not args.no_extras and world == 1 and args.layers == N_LAYERS
     stack, setup_s = build_stack(pkg, ref, max(rows, 2048 if want_extras else rows), band, dtype, args.layers)
     stack.set_lanes(lanes)
     stack.set_fusion(args.fusion)
@@ -381,16 +510,18 @@ def main():
         for _ in range(args.warmup):
             step()
     stream.synchronize()
-    ms, t0, t1 = time_steps(step, args.steps, stream, barrier)
-    clocks = sampler.summary(t0, t1)
+    # `repeats` timed passes of exactly `steps` steps, each bracketed by barrier + synchronize, each the max over ranks
+    pass_ms, t_first, t_last = [], None, None
+    for _ in range(args.repeats):
+        ms, t0, t1 = time_steps(step, args.steps, stream, barrier)
+        pass_ms.append(max_over_ranks(ms))
+        t_first = t0 if t_first is None else t_first
+        t_last = t1
+    clocks = sampler.summary(t_first, t_last)
     if pkg.poll_status() != 0:
         raise SystemExit("a GEMM kernel reported a bounded-wait timeout")
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ops_per_step = rows * OPS_PER_ROW_LAYER * args.layers * chained
-    total_rows = rows * world if args.workload != "cfg3" else CFG3_WORLDS * CFG3_ROWS_PER_WORLD
+    ms = statistics.median(pass_ms)
+    total_rows = rows * world if args.workload != "cfg3" else args.worlds * CFG3_ROWS_PER_WORLD
     job_ops_per_step = total_rows * OPS_PER_ROW_LAYER * args.layers * chained
     value = job_ops_per_step * args.steps / (ms * 1e-3) / 1e12
     launches = stack.launches_per_forward * args.steps
@@ -400,17 +531,16 @@ def main():
     yh = torch.empty_like(xh).pin_memory()
     for _ in range(3):
         stack.forward_host(xh, yh, steps=chained, use_graph=use_graph)
-    barrier()
-    torch.cuda.synchronize()
-    e0 = time.perf_counter()
-    for _ in range(args.steps):
-        stack.forward_host(xh, yh, steps=chained, use_graph=use_graph)
-    e_ms = (time.perf_counter() - e0) * 1e3
-    barrier()
-    if world > 1:
-        t = torch.tensor([e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e_ms = float(t.item())
+    e2e_ms = []
+    for _ in range(min(args.repeats, 3)):
+        barrier()
+        torch.cuda.synchronize()
+        e0 = time.perf_counter()
+        for _ in range(args.steps):
+            stack.forward_host(xh, yh, steps=chained, use_graph=use_graph)
+        e2e_ms.append(max_over_ranks((time.perf_counter() - e0) * 1e3))
+        barrier()
+    e_ms = statistics.median(e2e_ms)
     e2e_value = job_ops_per_step * args.steps / (e_ms * 1e-3) / 1e12
     io_bytes = rows * D_MODEL * 2
 
@@ -421,23 +551,30 @@ def main():
             dist.destroy_process_group()
         return 0
 
-    # roofline of the dominant kernel (the tcgen05 GEMM), timed per launch with CUDA events
-    per_launch = time_gemm_kernels(pkg, rows, stream)
-    gemm_ops = rows * OPS_PER_ROW_LAYER
+    # roofline of the dominant kernel (the tcgen05 GEMM), timed per launch with CUDA events at the
+    # height the stack launches it with (one band of rows)
+    launch_rows = min(rows, band) if band > 0 else rows
+    per_launch = time_gemm_kernels(pkg, launch_rows, stream)
+    gemm_ops = launch_rows * OPS_PER_ROW_LAYER
     gemm_s = sum(per_launch.values())
     int8_peak = 2.0 * peaks["bf16_tflops"]  # tcgen05 int8 issues at twice the bf16 rate
     achieved = gemm_ops / gemm_s / 1e12
     weight_gbs = WEIGHT_BYTES_LAYER / gemm_s / 1e9
-    # DRAM bytes of the five launches of one layer from the committed ncu capture (profiles/), M=512 only
-    traffic = NCU_DRAM_BYTES_PER_LAYER_M512 if rows == 512 else None
+    mma_burst, mma_sustained = pkg.mma_rate(16384), pkg.mma_rate(1 << 20)
+    traffic = NCU_DRAM_BYTES_PER_LAYER.get(launch_rows)
+    algo_bytes = layer_gemm_algorithmic_bytes(launch_rows)
     roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                 "frac": achieved / int8_peak, "traffic": traffic,
-                "traffic_note": "dram read+write summed over the five GEMM launches of one layer (ncu, profiles/"
-                                "gemm_i8_kernel_layer_m512.md); algorithmic bytes of the same launches: "
-                                f"{(WEIGHT_BYTES_LAYER + rows * (4 * D_MODEL + D_HIDDEN) + 3 * rows * D_MODEL * 2) / 1e6:.1f} MB",
-                "kernel": "gemm_i8_kernel (tcgen05 s8xs8->s32 + fused epilogue), five linears of a layer",
+                "traffic_note": "dram read+write summed over the five GEMM launches of one layer at this height (ncu, "
+                                f"profiles/); algorithmic bytes of the same launches: {algo_bytes / 1e6:.1f} MB",
+                "kernel": f"gemm_i8 (tcgen05 s8xs8->s32 + fused epilogue), five linears of a layer at M={launch_rows}",
                 "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}); nominal dense int8 4500",
                 "frac_of_nominal_4500": achieved / 4500.0,
+                "measured_int8_mma_tops": {"burst": mma_burst, "sustained": mma_sustained,
+                                           "how": "b200_w8a8_selftest_mma_rate: one CTA per SM issuing tcgen05.mma "
+                                                  "kind::i8 128x256x32 back to back, no loads, no epilogue"},
+                "frac_of_measured_int8_mma": achieved / mma_burst,
+                "frac_of_measured_int8_mma_sustained": achieved / mma_sustained,
                 "weight_stream_gbs": weight_gbs, "weight_stream_frac_of_hbm": weight_gbs / peaks["hbm_gbs"],
                 "us_per_launch": {k: v * 1e6 for k, v in per_launch.items()}}
 
@@ -445,11 +582,13 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong" if args.workload == "cfg3" else "weak", "vs_baseline": None, "dtype": "s8",
             "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {args.layers}-layer W8A8 linear stack, M={rows} rows per GPU, "
-                                   f"{chained} chained pass(es) per step, d=2048, qkv 6144, mlp 8192, {dt_name}",
+            "config": {"workload": workload_string(args.workload, args.layers, args.worlds),
                        "rows_per_gpu": rows, "layers": args.layers, "graph_replay": use_graph,
-                       "band_rows": band, "lanes": lanes,
-                       "l2": "no flush: each step streams 1.31 GB of int8 weights, 10x the 126 MB L2"},
+                       "band_rows": band, "lanes": lanes, "fused_quantizers": bool(args.fusion),
+                       "l2": "no flush: each step streams 1.31 GB of int8 weights per band, 10x the 126 MB L2"},
+            "timing": {"repeats": args.repeats, "ms_per_step_each": [m / args.steps for m in pass_ms],
+                       "statistic": "median of the repeats; each repeat = K steps between barrier + synchronize, "
+                                    "CUDA events, max over ranks"},
             "gpu_launches": int(launches), "clocks": clocks, "setup_s": setup_s,
             "e2e": {"value": e2e_value, "unit": "TOP/s", "ms_per_step": e_ms / args.steps,
                     "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
@@ -467,184 +606,59 @@ def main():
     return 0
 
 
-def run_only_gemms(pkg, rows, rounds):
-    import torch
-    dev = "cuda"
-    bufs = []
-    for name, n, k in LINEARS:
-        a8 = torch.randint(-127, 128, (rows, k), dtype=torch.int8, device=dev)
-        ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(rounds)]
-        sx, sw = torch.rand(rows, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-3
-        out = torch.empty(rows, n, dtype=torch.float32 if name == "up" else torch.float16, device=dev)
-        res = torch.randn(rows, n, device=dev).half() if n == D_MODEL else None
-        bufs.append((n, a8, ws, sx, sw, out, res, pkg.ACT_GELU_TANH if name == "up" else pkg.ACT_NONE))
-    for i in range(rounds):
-        for n, a8, ws, sx, sw, out, res, act in bufs:
-            pkg.linear(a8, sx, ws[i], sw, n=n, w_layout=pkg.W_SLAB128, residual=res, act=act, out=out,
-                       const_weights=True)
-    torch.cuda.synchronize()
-    print(json.dumps({"only_gemms_rows": rows, "rounds": rounds, "status": pkg.poll_status()}))
-    return 0
-
-
-def run_only_quant(pkg, rows, rounds):
-    import torch
-    dev = "cuda"
-    x = torch.randn(rows, D_MODEL, device=dev).half()
-    gamma = 1 + 0.05 * torch.randn(D_MODEL, device=dev)
-    qkv = torch.randn(rows, N_QKV, device=dev).half()
-    h = torch.randn(rows, D_HIDDEN, device=dev)
-    for _ in range(rounds):
-        pkg.rms_norm_quantize_rows(x, gamma, None, 1e-6, scale_is_mod=False)
-        pkg.quantize_rows(qkv, cols=D_MODEL)
-        pkg.quantize_rows(h)
-    torch.cuda.synchronize()
-    print(json.dumps({"only_quant_rows": rows, "rounds": rounds}))
-    return 0
-
-
-def run_only_grouped(pkg, rows, rounds, k=D_MODEL, n=D_HIDDEN, n_weights=N_LAYERS):
-    import torch
-    dev = "cuda"
-    ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(n_weights)]
-    a8 = torch.randint(-127, 128, (rows, k), dtype=torch.int8, device=dev)
-    sx, sw = torch.rand(rows, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-3
-    probs = [dict(x_i8=a8, x_scales=sx, w_i8=w, w_scales=sw, n=n,
-                  out=torch.empty(rows, n, dtype=torch.float16, device=dev)) for w in ws]
-    for _ in range(rounds):
-        pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
-    torch.cuda.synchronize()
-    print(json.dumps({"only_grouped_rows": rows, "rounds": rounds, "problems": n_weights, "status": pkg.poll_status()}))
-    return 0
-
-
-def run_only_qkv_heads(pkg, tokens, rounds, n_heads=32, n_kv_heads=16, d_head=64, k=D_MODEL):
-    import torch
-    dev = "cuda"
-    n = (n_heads + 2 * n_kv_heads) * d_head
-    g = torch.Generator().manual_seed(7)
-    ws = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(rounds)]
-    a8 = torch.randint(-127, 128, (tokens, k), dtype=torch.int8, device=dev)
-    sx, sw = torch.rand(tokens, device=dev) * 1e-2, torch.rand(n, device=dev) * 1e-3
-    pos = [torch.randint(0, hi, (tokens,), generator=g).to(dev) for hi in (32, 16, 64)]
-    xy = (torch.rand(d_head // 8, generator=g) * 6).to(dev)
-    inv_t = torch.rand(d_head // 2 - 2 * (d_head // 8), generator=g).to(dev)
-    cos, sin = pkg.rope_tables(*pos, xy, inv_t, d_head, 32, 16)
-    for w in ws:
-        pkg.linear_qkv_heads(a8, sx, w.view(n, k), sw, cos, sin, n_heads, n_kv_heads, d_head, 1e-6,
-                             w_layout=pkg.W_SLAB128)
-    torch.cuda.synchronize()
-    print(json.dumps({"only_qkv_heads_tokens": tokens, "rounds": rounds, "status": pkg.poll_status()}))
-    return 0
-
-
 def run_extras(pkg, ref, stack, stream, peaks):
-    """Secondary configs, each a short run: the chained M=2048 bf16 config, graph vs eager at M=512."""
+    """Secondary configs on one GPU, each a short run with the same stack: config 1 (M=512, one pass, graph
+    and eager, with the reference's CUDA operators at the same M beside it), config 2 (M=2048, four chained
+    passes, bf16), config 4 (skinny linears) and the QKV consumer epilogue."""
     import torch
     out = {}
+    stack.set_lanes(1)
+
+    def timed(x, y, steps, use_graph, reps):
+        fn = lambda: stack.forward(x, y, steps=steps, use_graph=use_graph, stream=stream.cuda_stream)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fn()
+        passes = [time_steps(fn, reps, stream, lambda: None)[0] / reps for _ in range(5)]
+        return statistics.median(passes), passes
+
     # config 2: M=2048, 4 chained passes, bf16
     stack.set_dtype(torch.bfloat16)
     x = ref.make_tokens(2048, 0, torch.bfloat16).to("cuda")
     y = torch.empty_like(x)
-    fn = lambda: stack.forward(x, y, steps=4, use_graph=True, stream=stream.cuda_stream)
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            fn()
-    ms, _, _ = time_steps(fn, 5, stream, lambda: None)
-    ops = 2048 * OPS_PER_ROW_LAYER * N_LAYERS * 4
-    tops = ops * 5 / (ms * 1e-3) / 1e12
-    out["cfg2_m2048_4steps_bf16"] = {"ms_per_4_steps": ms / 5, "tops": tops,
+    ms, passes = timed(x, y, 4, True, 5)
+    tops = 2048 * OPS_PER_ROW_LAYER * N_LAYERS * 4 / (ms * 1e-3) / 1e12
+    out["cfg2_m2048_4steps_bf16"] = {"ms_per_4_steps": ms, "ms_each": passes, "tops": tops,
                                      "frac_of_2x_measured_bf16": tops / (2 * peaks["bf16_tflops"]),
-                                     "frac_of_nominal_4500": tops / 4500.0}
-    # config 1 without graph replay
+                                     "frac_of_nominal_4500": tops / 4500.0,
+                                     "target": "<= 7.94 ms (60 % of 4500 TOP/s)"}
+    # config 1: M=512, one pass, fp16: graph replay and eager launches
     stack.set_dtype(torch.float16)
     x = ref.make_tokens(512, 0, torch.float16).to("cuda")
     y = torch.empty_like(x)
-    fn = lambda: stack.forward(x, y, steps=1, use_graph=False, stream=stream.cuda_stream)
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            fn()
-    ms, _, _ = time_steps(fn, 20, stream, lambda: None)
-    out["cfg1_eager_ms_per_step"] = ms / 20
+    ms_graph, passes = timed(x, y, 1, True, 20)
+    ms_eager, _ = timed(x, y, 1, False, 20)
+    ops1 = 512 * OPS_PER_ROW_LAYER * N_LAYERS
+    out["cfg1_m512_fp16"] = {"graph_ms_per_step": ms_graph, "graph_ms_each": passes, "eager_ms_per_step": ms_eager,
+                             "graph_tops": ops1 / (ms_graph * 1e-3) / 1e12, "eager_tops": ops1 / (ms_eager * 1e-3) / 1e12}
+    try:  # the reference's own CUDA operators at the same M, eager like the reference launches them
+        why_not = reference_cuda_available()
+        if why_not is None:
+            rstack = ReferenceCudaStack(512)
+            rstack.layers()
+            ms_ref = event_ms(rstack.layers, 3)
+            gemm_us = {}
+            for name, _, _ in LINEARS:
+                gemm_us[name] = event_ms(lambda name=name: [rstack.gemm(name, l) for l in range(N_LAYERS)], 3) / N_LAYERS * 1e3
+            out["cfg1_m512_fp16"]["reference_cuda_ops"] = {"eager_ms_per_step": ms_ref, "tops": ops1 / (ms_ref * 1e-3) / 1e12,
+                                                           "gemm_us": gemm_us, "launches_per_layer": 14}
+            del rstack
+        else:
+            out["cfg1_m512_fp16"]["reference_cuda_ops"] = {"unavailable": why_not}
+    except Exception as exc:  # a comparator must never cost the line
+        out["cfg1_m512_fp16"]["reference_cuda_ops"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     out["cfg4_skinny"] = run_skinny(pkg, stream, peaks)
     out["qkv_heads_t512"] = run_qkv_heads(pkg, stream)
-    return out
-
-
-def run_reference_cuda_ops(rows=512, n_heads=32, d_head=64):
-    """The reference's own CUDA operators (src/world_cuda_ops.cu compiled into oracle/_ref/, its
-    CUTLASS Sm80 mma.sync GEMM included) on this GPU: each of the five GEMM shapes into the int32
-    scratch, and the reference's per-layer operator sequence for the linears (norm->A8, GEMM, consumer /
-    dequant kernels; attention left out, as in the stack), with 24 distinct weight sets.  Launched one by
-    one on the default stream like the reference does (its operators take no stream), timed with events."""
-    import torch
-    sys.path.insert(0, str(ROOT / "oracle"))
-    import ref_cuda_ops as rk
-    if not rk.available():
-        return {"unavailable": "oracle/_ref/libworld_cuda_ops_ref.so is not built (needs the reference checkout "
-                               "and a CUTLASS header tree at build time)"}
-    dev = "cuda"
-    d, nq, hid = D_MODEL, N_QKV, D_HIDDEN
-    g = torch.Generator().manual_seed(11)
-    rnd8 = lambda *shape: torch.randint(-127, 128, shape, dtype=torch.int8, device=dev)
-    ws = {name: [rnd8(n, k) for _ in range(N_LAYERS)] for name, n, k in LINEARS}
-    sw = {name: torch.rand(n, device=dev) * 1e-3 for name, n, k in LINEARS}
-    x = torch.randn(rows, d, device=dev)
-    x1, x2, x3 = (torch.empty_like(x) for _ in range(3))
-    gamma = torch.randn(d, device=dev) * 0.05
-    gate = torch.ones(d, device=dev)
-    a8 = rnd8(rows, hid)
-    sa = torch.rand(rows, device=dev) * 1e-2
-    acc = torch.empty(rows, hid, dtype=torch.int32, device=dev)
-    n_kv = (nq // d_head - n_heads) // 2
-    q = torch.empty(n_heads, rows, d_head, device=dev)
-    kk = torch.empty(n_kv, rows, d_head, device=dev)
-    v = torch.empty(n_kv, rows, d_head, device=dev)
-    pos = [torch.randint(0, hi, (rows,), generator=g).to(dev) for hi in (32, 16, 64)]
-    xy = (torch.rand(d_head // 8, generator=g) * 6).to(dev)
-    inv_t = torch.rand(d_head // 2 - 2 * (d_head // 8), generator=g).to(dev)
-
-    def timed(fn, reps):
-        fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps * 1e3  # us
-
-    out = {"gemm_us": {}}
-    for name, n, k in LINEARS:
-        def gemms(name=name, n=n, k=k):
-            for w in ws[name]:
-                rk.call("gemm_i8_i32", a8, w, acc, rows, k, n)
-        out["gemm_us"][name] = timed(gemms, 3) / N_LAYERS
-
-    def layers():
-        for l in range(N_LAYERS):
-            rk.call("rms_norm_quantize_rows_i8", x, gamma, None, a8, sa, rows, d, 1e-6)
-            rk.call("gemm_i8_i32", a8, ws["qkv"][l], acc, rows, d, nq)
-            rk.call("qkv_fused_rms_rope_i32_dequant", acc, sa, sw["qkv"], q, kk, v, *pos, xy, inv_t, rows, n_heads,
-                    n_kv, d_head, 32, 16, 1e-6)
-            rk.call("quantize_rows_f32_i8", q, a8, sa, rows, d)  # stands in for the attention output [rows, d]
-            rk.call("gemm_i8_i32", a8, ws["out"][l], acc, rows, d, d)
-            rk.call("dequant_gated_residual_f32", acc, sa, sw["out"], x, gate, x1, rows, d)
-            rk.call("rms_norm_quantize_rows_i8", x1, gamma, None, a8, sa, rows, d, 1e-6)
-            rk.call("gemm_i8_i32", a8, ws["ctrl"][l], acc, rows, d, d)
-            rk.call("dequant_add_residual_f32", acc, sa, sw["ctrl"], x1, x2, rows, d)
-            rk.call("rms_norm_quantize_rows_i8", x2, gamma, None, a8, sa, rows, d, 1e-6)
-            rk.call("gemm_i8_i32", a8, ws["up"][l], acc, rows, d, hid)
-            rk.call("dequant_silu_quantize_rows_i8", acc, sa, sw["up"], None, a8, sa, rows, hid)
-            rk.call("gemm_i8_i32", a8, ws["down"][l], acc, rows, hid, d)
-            rk.call("dequant_gated_residual_f32", acc, sa, sw["down"], x2, gate, x3, rows, d)
-    us = timed(layers, 3)
-    out["stack_ms_per_step"] = us / 1e3
-    out["stack_tops"] = rows * OPS_PER_ROW_LAYER * N_LAYERS / (us * 1e-6) / 1e12
-    out["launches_per_layer"] = 14
-    out["note"] = (f"M={rows}, fp32 tokens, SiLU, gated residuals (the reference's operator set); eager launches on the "
-                   "default stream, built with the reference's --use_fast_math")
     return out
 
 

@@ -63,6 +63,12 @@ int b200_w8a8_poll_status(int *status_out);
 void b200_w8a8_debug_set_wait_limit_ns(unsigned long long ns);
 void b200_w8a8_debug_drop_operand_load(int launches);
 
+/* Self-test: the rate at which this device retires tcgen05.mma kind::i8 (128 x 256 x 32 per
+ * instruction) when one CTA per SM issues `slabs_per_cta` x 4 of them back to back with no operand
+ * loads and no epilogue, in tera-operations per second.  Blocks until done (a few milliseconds per
+ * 10 000 slabs).  The measured ceiling for any int8 GEMM on the part; no counterpart in the reference. */
+int b200_w8a8_selftest_mma_rate(int slabs_per_cta, double *tera_ops_per_s);
+
 /* ---- activation quantizers ------------------------------------------------------- */
 
 /* Per-row symmetric absmax int8 of rows of x (element type x_dtype, row stride ldx

@@ -46,6 +46,7 @@ _PROTOTYPES = {
     "b200_w8a8_linear_qkv_heads": (c_int, [c_void_p] * 3 + [c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_void_p]),
     "b200_w8a8_gemm_i8_i32_can_implement": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int]),
     "b200_w8a8_gemm_i8_i32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_w8a8_selftest_mma_rate": (c_int, [c_int, POINTER(ctypes.c_double)]),
     "b200_w8a8_debug_set_wait_limit_ns": (None, [ctypes.c_ulonglong]),
     "b200_w8a8_debug_drop_operand_load": (None, [c_int]),
     "b200_w8a8_debug_force_plan": (None, [c_int, c_int, c_int]),
@@ -129,6 +130,13 @@ def _stream():
 def _dt(t) -> int:
     import torch
     return {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16, torch.int32: DT_S32}[t.dtype]
+
+
+def mma_rate(slabs_per_cta=16384) -> float:
+    """Measured tcgen05 int8 MMA rate of the current device in TOP/s (see b200_w8a8_selftest_mma_rate)."""
+    out = ctypes.c_double(0.0)
+    _check(lib().b200_w8a8_selftest_mma_rate(slabs_per_cta, ctypes.byref(out)), "selftest_mma_rate")
+    return out.value
 
 
 def poll_status() -> int:

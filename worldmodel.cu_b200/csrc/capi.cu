@@ -46,6 +46,10 @@ extern "C" {
 int b200_w8a8_abi_version(void) { return B200_W8A8_ABI_VERSION; }
 const char *b200_w8a8_last_error(void) { return last_error_message(); }
 int b200_w8a8_poll_status(int *status_out) { return status_poll(status_out); }
+int b200_w8a8_selftest_mma_rate(int slabs_per_cta, double *tera_ops_per_s) {
+    if (status_check_entry()) return 1;
+    return mma_issue_rate(slabs_per_cta, tera_ops_per_s);
+}
 void b200_w8a8_debug_set_wait_limit_ns(unsigned long long ns) { set_wait_limit_ns(ns); }
 void b200_w8a8_debug_drop_operand_load(int launches) { debug_drop_a_loads(launches); }
 void b200_w8a8_debug_force_plan(int tile_width, int k_splits, int split_mode) {

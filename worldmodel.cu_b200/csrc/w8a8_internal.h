@@ -174,6 +174,9 @@ void gemm_set_trace_buffer(unsigned long long *dev_buf);
 unsigned long long *gemm_trace_buffer();
 void gemm_force_plan(int bn, int splits, int mode);
 
+// ---- mma_rate.cu
+int mma_issue_rate(int slabs_per_cta, double *tera_ops_per_s);
+
 // ---- pack_weights.cpp
 int pack_weight_host(const float *w, int n, int k, int layout, int8_t *packed, float *scales, int threads);
 size_t packed_weight_bytes(int n, int k, int layout);
