@@ -332,6 +332,41 @@ size_t b200_w8a8_stack_device_bytes(void *stack);
 /* Kernels enqueued (or replayed) by the most recent forward. */
 long long b200_w8a8_stack_launches_per_forward(void *stack);
 
+/* ---- one layer in the reference's parameterization (host-side driver above the operators) -------- */
+
+/* Device pointers of one WorldDiT layer, owned by the caller: int8 weights [N,K] with their
+ * per-channel scales and the per-layer vectors (the fields the reference keeps per layer in
+ * src/world_cuda_internal.cuh:16-39 plus the modulation rows of src/world_cuda.cu:737-770).
+ * w_ctrl_fc1 == NULL means the layer has no controller branch (has_ctrl, src/world_cuda.cu:2106). */
+typedef struct {
+    const int8_t *w_qkv;      const float *s_qkv;       /* [(Hq + 2 Hkv) * d_head, D] */
+    const int8_t *w_out;      const float *s_out;       /* [D, D] */
+    const int8_t *w_ctrl_fc1; const float *s_ctrl_fc1;  /* [D, D] */
+    const int8_t *w_ctrl_fc2; const float *s_ctrl_fc2;  /* [D, D] */
+    const int8_t *w_fc1;      const float *s_fc1;       /* [hidden, D] */
+    const int8_t *w_fc2;      const float *s_fc2;       /* [D, hidden] */
+    const float *mod_scale0, *mod_bias0, *gate0;        /* [D]: AdaRMSNorm before QKV (nullable), gate of the attention residual */
+    const float *ctrl_cond;                             /* [D]: added before the controller's SiLU, nullable */
+    const float *mod_scale1, *mod_bias1, *gate1;        /* [D]: AdaRMSNorm before the MLP (nullable), gate of the MLP residual */
+} b200_w8a8_layer;
+
+/* The W8A8 linears of one layer as two calls around the caller's attention, fp32 token stream,
+ * SiLU, gated residuals, controller branch: what world_cuda_runtime_step_rgb does per layer
+ * (src/world_cuda.cu:1819-1882 and 2058-2330) with each quantize -> int8 GEMM -> dequant triple
+ * fused into one GEMM launch -- 13 launches per layer instead of 16 and no T x hidden int32 scratch.
+ * The context owns activation scratch for up to max_tokens rows (device_bytes reports it); weights are
+ * read in `w_layout` where the caller keeps them.  d_head must be 64 (see b200_w8a8_linear_qkv_heads)
+ * and n_heads * d_head == d_model.  rope_cos / rope_sin come from b200_w8a8_rope_tables, once per frame.
+ * tokens_next may be the same buffer as tokens. */
+void *b200_w8a8_layer_ctx_create(int max_tokens, int d_model, int n_heads, int n_kv_heads, int d_head, int d_hidden,
+                                 float eps, int w_layout);
+void b200_w8a8_layer_ctx_destroy(void *ctx);
+size_t b200_w8a8_layer_ctx_device_bytes(void *ctx);
+int b200_w8a8_layer_qkv(void *ctx, const b200_w8a8_layer *layer, const float *tokens, const float *rope_cos,
+                        const float *rope_sin, float *q, float *k, float *v, int n_tokens, void *stream);
+int b200_w8a8_layer_after_attention(void *ctx, const b200_w8a8_layer *layer, const float *attn, const float *tokens,
+                                    float *tokens_next, int n_tokens, void *stream);
+
 /* ---- offline packed-weight file (HOST side; the writer needs no GPU) ---------------- */
 
 /* Writes the int8 codes (slab layout) and per-channel scales of every layer, plus the three

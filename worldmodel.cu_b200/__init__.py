@@ -80,6 +80,11 @@ _PROTOTYPES = {
     "b200_w8a8_stack_set_fusion": (c_int, [c_void_p, c_int]),
     "b200_w8a8_stack_device_bytes": (c_size_t, [c_void_p]),
     "b200_w8a8_stack_launches_per_forward": (ctypes.c_longlong, [c_void_p]),
+    "b200_w8a8_layer_ctx_create": (c_void_p, [c_int] * 6 + [c_float, c_int]),
+    "b200_w8a8_layer_ctx_destroy": (None, [c_void_p]),
+    "b200_w8a8_layer_ctx_device_bytes": (c_size_t, [c_void_p]),
+    "b200_w8a8_layer_qkv": (c_int, [c_void_p] * 8 + [c_int, c_void_p]),
+    "b200_w8a8_layer_after_attention": (c_int, [c_void_p] * 5 + [c_int, c_void_p]),
     "b200_w8a8_weight_file_create": (c_void_p, [ctypes.c_char_p, c_int, c_int, c_int, c_int]),
     "b200_w8a8_weight_file_add_layer": (c_int, [c_void_p] + [c_void_p] * 8 + [c_int]),
     "b200_w8a8_weight_file_close": (c_int, [c_void_p]),
@@ -372,6 +377,63 @@ def weight_file_info(path, verify=True):
     _check(lib().b200_w8a8_weight_file_info(str(path).encode(), *[ctypes.byref(v) for v in vals], int(verify)),
            "weight_file_info")
     return tuple(v.value for v in vals)
+
+
+class _Layer(ctypes.Structure):
+    """b200_w8a8_layer of include/b200_w8a8.h."""
+    _fields_ = [(n, c_void_p) for n in ("w_qkv", "s_qkv", "w_out", "s_out", "w_ctrl_fc1", "s_ctrl_fc1", "w_ctrl_fc2",
+                                        "s_ctrl_fc2", "w_fc1", "s_fc1", "w_fc2", "s_fc2", "mod_scale0", "mod_bias0",
+                                        "gate0", "ctrl_cond", "mod_scale1", "mod_bias1", "gate1")]
+
+
+class ReferenceLayerDriver:
+    """The per-layer driver in the reference's parameterization (b200_w8a8_layer_*).  `layer` arguments are
+    dicts of CUDA tensors keyed like the fields of b200_w8a8_layer; missing keys are NULL."""
+
+    def __init__(self, max_tokens, d_model, n_heads, n_kv_heads, d_head, d_hidden, eps, w_layout=W_ROW_MAJOR):
+        self.dims = (d_model, n_heads, n_kv_heads, d_head, d_hidden)
+        self.handle = lib().b200_w8a8_layer_ctx_create(max_tokens, d_model, n_heads, n_kv_heads, d_head, d_hidden, eps,
+                                                       w_layout)
+        if not self.handle:
+            raise W8A8Error("layer_ctx_create failed: " + lib().b200_w8a8_last_error().decode())
+
+    @staticmethod
+    def pack(layer):
+        keep = dict(layer)  # keeps the tensors alive as long as the struct
+        st = _Layer(**{n: _ptr(layer.get(n)) for n, _ in _Layer._fields_})
+        st._keep = keep
+        return st
+
+    def qkv(self, layer, tokens, rope_cos, rope_sin):
+        import torch
+        d, hq, hkv, dh, _ = self.dims
+        T = tokens.shape[0]
+        q = torch.empty(hq, T, dh, dtype=torch.float32, device=tokens.device)
+        k = torch.empty(hkv, T, dh, dtype=torch.float32, device=tokens.device)
+        v = torch.empty(hkv, T, dh, dtype=torch.float32, device=tokens.device)
+        st = layer if isinstance(layer, _Layer) else self.pack(layer)
+        _check(lib().b200_w8a8_layer_qkv(self.handle, ctypes.byref(st), _ptr(tokens), _ptr(rope_cos), _ptr(rope_sin),
+                                         _ptr(q), _ptr(k), _ptr(v), T, _stream()), "layer_qkv")
+        return q, k, v
+
+    def after_attention(self, layer, attn, tokens, out=None):
+        import torch
+        out = torch.empty_like(tokens) if out is None else out
+        st = layer if isinstance(layer, _Layer) else self.pack(layer)
+        _check(lib().b200_w8a8_layer_after_attention(self.handle, ctypes.byref(st), _ptr(attn), _ptr(tokens), _ptr(out),
+                                                     tokens.shape[0], _stream()), "layer_after_attention")
+        return out
+
+    def close(self):
+        if self.handle:
+            lib().b200_w8a8_layer_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class LinearStack:

@@ -29,6 +29,7 @@ SOURCES = [
     "weight_file.cpp",
     "dropin.cu",
     "linear_stack.cu",
+    "layer_driver.cu",
 ]
 
 NVCC_FLAGS = [
