@@ -274,6 +274,31 @@ class ReferenceCudaStack:
             rk.call("dequant_gated_residual_f32", acc, sa, sw["down"], x2, self.gate, x3, rows, d)
 
 
+    def layers_reference_wiring(self, n_layers=N_LAYERS):
+        """The reference's real layer: six GEMMs (the controller branch is fc1 + cond -> SiLU -> fc2), sixteen
+        launches, as world_cuda_runtime_step_rgb issues them (src/world_cuda.cu:1819-2330)."""
+        rk, rows, d, nq, hid = self.rk, self.rows, D_MODEL, N_QKV, D_HIDDEN
+        x, x1, x2, x3, a8, sa, acc, sw = self.x, self.x1, self.x2, self.x3, self.a8, self.sa, self.acc, self.sw
+        for l in range(n_layers):
+            rk.call("rms_norm_quantize_rows_i8", x, self.gamma, self.gamma, a8, sa, rows, d, 1e-6)
+            self.gemm("qkv", l)
+            rk.call("qkv_fused_rms_rope_i32_dequant", acc, sa, sw["qkv"], self.q, self.k, self.v, *self.pos, self.xy,
+                    self.inv_t, rows, self.n_heads, self.n_kv, self.d_head, 32, 16, 1e-6)
+            rk.call("quantize_rows_f32_i8", self.q, a8, sa, rows, d)  # stands in for the attention output [rows, d]
+            self.gemm("out", l)
+            rk.call("dequant_gated_residual_f32", acc, sa, sw["out"], x, self.gate, x1, rows, d)
+            rk.call("rms_norm_quantize_rows_i8", x1, None, None, a8, sa, rows, d, 1e-6)
+            self.gemm("ctrl", l)
+            rk.call("dequant_silu_quantize_rows_i8", acc, sa, sw["ctrl"], self.gamma, a8, sa, rows, d)
+            self.gemm("ctrl", (l + 1) % N_LAYERS)
+            rk.call("dequant_add_residual_f32", acc, sa, sw["ctrl"], x1, x2, rows, d)
+            rk.call("rms_norm_quantize_rows_i8", x2, self.gamma, self.gamma, a8, sa, rows, d, 1e-6)
+            self.gemm("up", l)
+            rk.call("dequant_silu_quantize_rows_i8", acc, sa, sw["up"], None, a8, sa, rows, hid)
+            self.gemm("down", l)
+            rk.call("dequant_gated_residual_f32", acc, sa, sw["down"], x2, self.gate, x3, rows, d)
+
+
 def reference_cuda_available():
     import torch
     if not torch.cuda.is_available():
@@ -659,6 +684,83 @@ def run_extras(pkg, ref, stack, stream, peaks):
         out["cfg1_m512_fp16"]["reference_cuda_ops"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     out["cfg4_skinny"] = run_skinny(pkg, stream, peaks)
     out["qkv_heads_t512"] = run_qkv_heads(pkg, stream)
+    try:
+        out["reference_layer_t512"] = run_reference_layer(pkg, stream)
+    except Exception as exc:
+        out["reference_layer_t512"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    return out
+
+
+def run_reference_layer(pkg, stream, tokens=512, n_heads=32, d_head=64):
+    """The per-layer driver in the reference's parameterization (b200_w8a8_layer_qkv + _after_attention: AdaRMSNorm,
+    head-major q/k/v with RoPE, gated residuals, controller branch, SiLU MLP, fp32 tokens; 13 launches per layer)
+    over 24 distinct layers at T=512, next to the reference's own operators in the reference's own order
+    (16 launches per layer) on the same GPU.  The q block stands in for the attention output in both."""
+    import torch
+    dev = "cuda"
+    d, hid = D_MODEL, D_HIDDEN
+    n_kv = (N_QKV // d_head - n_heads) // 2
+    g = torch.Generator().manual_seed(21)
+    rnd8 = lambda n, k: torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev)
+    vec = lambda n, s=1e-3: torch.rand(n, device=dev) * s
+    layers = []
+    for _ in range(N_LAYERS):
+        layers.append(dict(w_qkv=rnd8(N_QKV, d), s_qkv=vec(N_QKV), w_out=rnd8(d, d), s_out=vec(d), w_ctrl_fc1=rnd8(d, d),
+                           s_ctrl_fc1=vec(d), w_ctrl_fc2=rnd8(d, d), s_ctrl_fc2=vec(d), w_fc1=rnd8(hid, d), s_fc1=vec(hid),
+                           w_fc2=rnd8(d, hid), s_fc2=vec(d, 1e-4), mod_scale0=vec(d, 0.1), mod_bias0=vec(d, 0.1),
+                           gate0=vec(d, 1.0), ctrl_cond=vec(d, 0.1), mod_scale1=vec(d, 0.1), mod_bias1=vec(d, 0.1),
+                           gate1=vec(d, 1.0)))
+    drv = pkg.ReferenceLayerDriver(tokens, d, n_heads, n_kv, d_head, hid, 1e-6, w_layout=pkg.W_SLAB128)
+    packed = [drv.pack(L) for L in layers]
+    pos = [torch.randint(0, hi, (tokens,), generator=g).to(dev) for hi in (32, 16, 64)]
+    xy = (torch.rand(d_head // 8, generator=g) * 6).to(dev)
+    inv_t = torch.rand(d_head // 2 - 2 * (d_head // 8), generator=g).to(dev)
+    x = torch.randn(tokens, d, device=dev)
+    bufs = [torch.empty_like(x), torch.empty_like(x)]
+    q = torch.empty(n_heads, tokens, d_head, device=dev)
+    k = torch.empty(n_kv, tokens, d_head, device=dev)
+    v = torch.empty(n_kv, tokens, d_head, device=dev)
+    L = pkg.lib()
+    import ctypes
+    with torch.cuda.stream(stream):
+        cos, sin = pkg.rope_tables(*pos, xy, inv_t, d_head, 32, 16)
+
+    def step():
+        st = torch.cuda.current_stream().cuda_stream
+        cur = x
+        for i, pl in enumerate(packed):
+            nxt = bufs[i & 1]
+            rc = L.b200_w8a8_layer_qkv(drv.handle, ctypes.byref(pl), cur.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                       q.data_ptr(), k.data_ptr(), v.data_ptr(), tokens, st)
+            rc |= L.b200_w8a8_layer_after_attention(drv.handle, ctypes.byref(pl), q.data_ptr(), cur.data_ptr(),
+                                                    nxt.data_ptr(), tokens, st)
+            assert rc == 0, L.b200_w8a8_last_error()
+            cur = nxt
+
+    with torch.cuda.stream(stream):
+        step()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step()
+    with torch.cuda.stream(stream):
+        graph.replay()
+    passes = [time_steps(graph.replay, 10, stream, lambda: None)[0] / 10 for _ in range(5)]
+    eager = [time_steps(step, 10, stream, lambda: None)[0] / 10 for _ in range(3)]
+    ops = tokens * 2 * (N_QKV * d + 3 * d * d + 2 * hid * d) * N_LAYERS
+    out = {"graph_ms_per_step": statistics.median(passes), "eager_ms_per_step": statistics.median(eager),
+           "launches_per_layer": 13, "tops_graph": ops / (statistics.median(passes) * 1e-3) / 1e12,
+           "shape": f"T={tokens} d={d} heads {n_heads}/{n_kv} x {d_head} hidden {hid}, 24 layers, SLAB128 weights"}
+    why_not = reference_cuda_available()
+    if why_not is None:
+        rstack = ReferenceCudaStack(tokens)
+        rstack.layers_reference_wiring()
+        ms_ref = event_ms(rstack.layers_reference_wiring, 3)
+        out["reference_cuda_ops"] = {"eager_ms_per_step": ms_ref, "launches_per_layer": 16,
+                                     "tops": ops / (ms_ref * 1e-3) / 1e12}
+    else:
+        out["reference_cuda_ops"] = {"unavailable": why_not}
+    drv.close()
     return out
 
 
@@ -747,15 +849,15 @@ def run_skinny(pkg, stream, peaks, n_weights=72):
             ms, _, _ = time_steps(graph.replay, 3, stream, lambda: None)
             us = ms / (3 * n_weights) * 1e3
             gbs = (n * k + m * k + 2 * m * n) / us / 1e3
-            # the same 72 linears as independent problems of one grouped call (two launches of <= 48 problems)
+            # the same 72 linears as independent problems of one grouped call (72 problems fit one launch)
             ys = [torch.empty(m, n, dtype=torch.float16, device=dev) for _ in ws]
             probs = [dict(x_i8=a8, x_scales=sx, w_i8=w, w_scales=sw, n=n, out=yy) for w, yy in zip(ws, ys)]
             with torch.cuda.stream(stream):
-                pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
+                pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16, const_weights=True)
             stream.synchronize()
             ggraph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(ggraph, stream=stream):
-                pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
+                pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16, const_weights=True)
             with torch.cuda.stream(stream):
                 ggraph.replay()
             gms, _, _ = time_steps(ggraph.replay, 3, stream, lambda: None)

@@ -268,6 +268,10 @@ typedef struct {
 } b200_w8a8_problem;
 int b200_w8a8_linear_grouped(const b200_w8a8_problem *problems_host, int count, int w_layout, int act, int y_dtype,
                              void *stream);
+/* Same for weights that no work queued on `stream` writes (see b200_w8a8_linear_const_weights): every CTA
+ * requests the weight tiles of its first tile while the previous kernel of the stream is still draining. */
+int b200_w8a8_linear_grouped_const_weights(const b200_w8a8_problem *problems_host, int count, int w_layout, int act,
+                                           int y_dtype, void *stream);
 
 /* ---- weights (HOST pointers) ------------------------------------------------------ */
 

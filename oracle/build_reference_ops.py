@@ -31,7 +31,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT_DIR = HERE / "_ref"
 LIB = OUT_DIR / "libworld_cuda_ops_ref.so"
-DEFAULT_REFERENCE = Path("/root/reference")
+# the reference checkout: $WORLDMODEL_REFERENCE_DIR, else a directory named `reference` beside this repository
+DEFAULT_REFERENCE = Path(os.environ.get("WORLDMODEL_REFERENCE_DIR") or HERE.parent.parent / "reference")
 CUTLASS_CANDIDATES = ("flashinfer/data/cutlass/include", "tilelang/3rdparty/cutlass/include",
                       "deep_gemm/include")
 

@@ -1,11 +1,12 @@
 """Generates tests/golden/w8a8_reference_golden.npz from the reference's own PyTorch helpers.
 
-Run once in a container that has the reference checkout:
+Run once on a machine that has the reference checkout:
     python tests/golden/make_golden.py /path/to/reference
+(without an argument: $WORLDMODEL_REFERENCE_DIR, else a directory named `reference` beside this repository)
 It imports tools/tests/test_w8a8_quantization.py from that checkout (the reference's
 "PyTorch parity reference"), runs its private helpers `_symmetric_quantize_rows` and
-`_w8a8_linear_reference` on seeded inputs and stores inputs and outputs.  The GPU box has
-no reference checkout; tests read only the committed .npz.
+`_w8a8_linear_reference` on seeded inputs and stores inputs and outputs.  Tests read only the
+committed .npz, so they run where no reference checkout exists.
 """
 import importlib.util
 import sys
@@ -24,7 +25,9 @@ def load_reference(root: Path):
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+    default = os.environ.get("WORLDMODEL_REFERENCE_DIR") or Path(__file__).resolve().parents[3] / "reference"
+    root = Path(sys.argv[1] if len(sys.argv) > 1 else default)
     ref = load_reference(root)
     out = {"torch_version": np.array(torch.__version__)}
 

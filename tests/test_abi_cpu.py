@@ -10,8 +10,11 @@ import numpy as np
 import pytest
 import torch
 
+import os
+
 ROOT = Path(__file__).resolve().parent.parent
-REFERENCE_HEADER = Path("/root/reference/src/world_cuda_ops.cuh")
+# the reference checkout: $WORLDMODEL_REFERENCE_DIR, else a directory named `reference` beside this repository
+REFERENCE_HEADER = Path(os.environ.get("WORLDMODEL_REFERENCE_DIR") or ROOT.parent / "reference") / "src" / "world_cuda_ops.cuh"
 
 
 def declared_symbols():

@@ -162,8 +162,11 @@ def test_config4_all_shapes_in_one_grouped_launch(pkg, ref):
         packed = qw.view(n, k // 128, 128).permute(1, 0, 2).contiguous()
         probs.append(dict(x_i8=qx.to(DEV), x_scales=sx.to(DEV), w_i8=packed.to(DEV), w_scales=sw.to(DEV), n=n))
         wants.append(ref.linear_w8a8(qx, sx, qw, sw, out_dtype=torch.float16))
-    outs = pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
+    outs = pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16, const_weights=True)
+    outs2 = pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16)
     torch.cuda.synchronize()
+    for a, b in zip(outs, outs2):
+        assert same(a, b)
     assert pkg.poll_status() == 0
     for y, want in zip(outs, wants):
         assert same(y, want)

@@ -59,9 +59,10 @@ def test_grouped_equals_single_linears_and_the_oracle(pkg, ref, out_dtype, act, 
 
 
 def test_grouped_more_problems_than_one_launch_holds(pkg, ref):
-    """72 problems (three shapes, 24 weight sets each): more than the 48 a launch takes."""
+    """150 problems (three shapes, 50 weight sets each): more than the 72 one launch takes, cut into
+    launches of about equal work."""
     probs = []
-    for i in range(72):
+    for i in range(150):
         m, k, n = [(16, 2048, 2048), (128, 256, 1024), (64, 512, 768)][i % 3]
         q, _ = make_problem(ref, m, k, n, 500 + i, torch.float16, bias=False, residual=False, use_slab=True)
         probs.append(q)

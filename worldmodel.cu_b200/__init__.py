@@ -42,6 +42,7 @@ _PROTOTYPES = {
                                            c_int, c_int, c_void_p]),
     "b200_w8a8_qkv_rms_rope_dequant": (c_int, [c_void_p] * 11 + [c_int] * 6 + [c_float, c_void_p]),
     "b200_w8a8_linear_grouped": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_w8a8_linear_grouped_const_weights": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_rope_tables": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_void_p] * 3),
     "b200_w8a8_linear_qkv_heads": (c_int, [c_void_p] * 3 + [c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_void_p]),
     "b200_w8a8_gemm_i8_i32_can_implement": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int]),
@@ -217,7 +218,7 @@ class _Problem(ctypes.Structure):
                 ("ldy", ctypes.c_int64), ("m", c_int), ("k", c_int), ("n", c_int)]
 
 
-def linear_grouped(problems, w_layout=W_ROW_MAJOR, act=ACT_NONE, out_dtype=None, stream=None):
+def linear_grouped(problems, w_layout=W_ROW_MAJOR, act=ACT_NONE, out_dtype=None, stream=None, const_weights=False):
     """Runs several independent skinny linears (M <= 128) in one launch.  `problems` is a list of dicts with
     keys x_i8, x_scales, w_i8, w_scales, n and optionally bias, residual, out; returns the list of outputs."""
     import torch
@@ -235,8 +236,9 @@ def linear_grouped(problems, w_layout=W_ROW_MAJOR, act=ACT_NONE, out_dtype=None,
         arr[i] = _Problem(_ptr(q["x_i8"]), _ptr(q["x_scales"]), _ptr(q["w_i8"]), _ptr(q["w_scales"]), _ptr(q.get("bias")),
                           _ptr(res), res.stride(0) if res is not None else 0, _ptr(y), y.stride(0), m, k, n)
     st = stream if stream is not None else _stream()
-    _check(lib().b200_w8a8_linear_grouped(ctypes.cast(arr, c_void_p), len(problems), w_layout, act, _dt(outs[0]) if outs
-                                          else DT_F16, st), "linear_grouped")
+    fn = lib().b200_w8a8_linear_grouped_const_weights if const_weights else lib().b200_w8a8_linear_grouped
+    _check(fn(ctypes.cast(arr, c_void_p), len(problems), w_layout, act, _dt(outs[0]) if outs else DT_F16, st),
+           "linear_grouped")
     return outs
 
 

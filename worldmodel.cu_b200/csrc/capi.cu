@@ -125,6 +125,13 @@ int b200_w8a8_linear_grouped(const b200_w8a8_problem *problems_host, int count, 
                           as_stream(stream));
 }
 
+int b200_w8a8_linear_grouped_const_weights(const b200_w8a8_problem *problems_host, int count, int w_layout, int act,
+                                           int y_dtype, void *stream) {
+    if (status_check_entry()) return 1;
+    return linear_grouped(reinterpret_cast<const GroupedLinear *>(problems_host), count, w_layout, act, y_dtype,
+                          as_stream(stream), 1);
+}
+
 static LinearArgs raw_gemm_args(const int8_t *x, const int8_t *w, int w_layout, const int32_t *acc, int m, int k,
                                 int n) {
     LinearArgs a{};

@@ -789,24 +789,28 @@ __global__ void __launch_bounds__(kThreads, 1)
 // being finished.  Every problem has a single block of rows (M <= 128); its A rows are loaded as
 // they are (ceil16(M) rows), the MMA spans 128 lanes and the lanes beyond M are never read back.
 // Problem descriptors and the two tensor maps of each problem travel in kernel-parameter space.
-constexpr int kMaxGroup = 48;  // 48 x (3 tensor maps + 80 bytes) = 22 KB of the 32 KB a kernel may take as parameters
+// 72 x (3 tensor maps of 128 bytes + a 64-byte record) + a 40-byte header = 32 296 of the 32 764 bytes a
+// kernel may take as parameters.
+constexpr int kMaxGroup = 72;
 struct GroupedProblem {
     const float *row_scales, *col_scales, *bias;
     const void *residual;
     void *out;
-    long long ldo, ldr;
-    int m, n, k_blocks;
-    int a_bytes;  // bytes one A copy delivers: ceil16(m) * 128
-    int tile0;    // index of the problem's first tile in the launch-wide sequence
-    int vec_ok;
-    int tma_store;  // the output is aligned for bulk-tensor stores (else plain stores)
+    int ldo, ldr;   // row strides in elements (below 2^31)
+    int m, n;
+    int tile0;      // index of the problem's first tile in the launch-wide sequence
+    unsigned short k_blocks;  // K slabs of 128 bytes (K <= 8 388 480)
+    unsigned char vec_ok;     // 16-byte vector access to the per-column vectors / residual is legal
+    unsigned char tma_store;  // the output is aligned for bulk-tensor stores (else plain stores)
 };
+static_assert(sizeof(GroupedProblem) == 64, "the grouped problem record is sized to fit 72 per launch");
 struct GroupedParams {
     CUtensorMap tm_a[kMaxGroup];
     CUtensorMap tm_w[kMaxGroup];
     CUtensorMap tm_out[kMaxGroup];
     GroupedProblem prob[kMaxGroup];
     int count, total_tiles, act, out_dtype, w_kx, w_kz;
+    int static_weights;  // W may be fetched before the predecessor kernel has completed
     int *status;
     unsigned long long wait_limit_ns;
 };
@@ -853,21 +857,41 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
 
     if (warp == 0) {
         if (lane == 0) {
-            pdl_wait();
             int s = 0, g = 0;
             uint32_t ph = 0;
             bool ok = true;
+            // weights nothing in the stream writes: the first ring of W tiles of this CTA's first tile goes out
+            // before the predecessor kernel has finished; the A tiles follow once it has
+            int prefetched = 0;
+            if (gp.static_weights && (int)blockIdx.x < gp.total_tiles) {
+                int g0 = 0;
+                while (g0 + 1 < gp.count && (int)blockIdx.x >= gp.prob[g0 + 1].tile0) ++g0;
+                const GroupedProblem &q = gp.prob[g0];
+                const int n0 = ((int)blockIdx.x - q.tile0) * BN;
+                prefetched = min((int)q.k_blocks, C::kStages);
+                for (int i = 0; i < prefetched; ++i) {
+                    uint8_t *sa = smem + i * C::kStageBytes;
+                    mbar_arrive_expect_tx(&bar_full[i], (uint32_t)(((q.m + 15) / 16) * 16 * BK + C::kBBytes));
+                    tma_load_3d(sa + C::kABytes, &gp.tm_w[g0], &bar_full[i], i * gp.w_kx, n0, i * gp.w_kz);
+                }
+            }
+            pdl_wait();
             for (int work = blockIdx.x; ok && work < gp.total_tiles; work += gridDim.x) {
                 while (g + 1 < gp.count && work >= gp.prob[g + 1].tile0) ++g;  // tiles are visited in order
                 const GroupedProblem &q = gp.prob[g];
                 const int n0 = (work - q.tile0) * BN;
                 for (int kb = 0; kb < q.k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
-                    if (!ok) break;
                     uint8_t *sa = smem + s * C::kStageBytes;
-                    mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(q.a_bytes + C::kBBytes));
-                    tma_load_3d(sa, &gp.tm_a[g], &bar_full[s], kb * BK, 0, 0);
-                    tma_load_3d(sa + C::kABytes, &gp.tm_w[g], &bar_full[s], kb * gp.w_kx, n0, kb * gp.w_kz);
+                    if (prefetched > 0) {  // stage already armed, its W tile already requested
+                        --prefetched;
+                        tma_load_3d(sa, &gp.tm_a[g], &bar_full[s], kb * BK, 0, 0);
+                    } else {
+                        ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(((q.m + 15) / 16) * 16 * BK + C::kBBytes));
+                        tma_load_3d(sa, &gp.tm_a[g], &bar_full[s], kb * BK, 0, 0);
+                        tma_load_3d(sa + C::kABytes, &gp.tm_w[g], &bar_full[s], kb * gp.w_kx, n0, kb * gp.w_kz);
+                    }
                     if (++s == C::kStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -1322,7 +1346,7 @@ int linear_qkv_heads(const QkvHeadsArgs &q, cudaStream_t stream) {
 }
 
 int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int act, int out_dtype,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, int static_weights) {
     if (count == 0) return 0;
     if (!problems || count < 0) return fail("invalid linear_grouped arguments count=%d", count);
     if (out_dtype != B200_DT_F32 && out_dtype != B200_DT_F16 && out_dtype != B200_DT_BF16)
@@ -1338,12 +1362,36 @@ int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int a
     if (oi == 1 && ensure_smem_attr(di.grouped_attr_set[1], gemm_i8_grouped_kernel<B200_DT_F16>, C::kSmemBytes, "grouped")) return 1;
     if (oi == 2 && ensure_smem_attr(di.grouped_attr_set[2], gemm_i8_grouped_kernel<B200_DT_BF16>, C::kSmemBytes, "grouped")) return 1;
     const size_t esz = out_dtype == B200_DT_F32 ? 4 : 2;
-    static thread_local GroupedParams gp;  // 16 KB: kept off the stack
-    for (int first = 0; first < count; first += kMaxGroup) {
-        const int n_here = count - first < kMaxGroup ? count - first : kMaxGroup;
+    static thread_local GroupedParams gp;  // 32 KB: kept off the stack
+    static_assert(sizeof(GroupedParams) <= 32764, "kernel parameters are limited to 32 764 bytes");
+    // A group larger than one launch can describe is cut into launches of about equal work (tiles x K
+    // slabs), not into "as many problems as fit, then the rest": a short last launch leaves most SMs
+    // idle for its final round (72 problems of 8 tiles as 48 + 24 ran 5 rounds of tiles for 3.9 rounds of
+    // work; as 36 + 36 they run 4).
+    const int n_launches = (count + kMaxGroup - 1) / kMaxGroup;
+    double total_work = 0.0;
+    for (int i = 0; i < count; ++i)
+        if (problems[i].n > 0 && problems[i].k > 0)
+            total_work += (double)((problems[i].n + 255) / 256) * (double)((problems[i].k + BK - 1) / BK);
+    double work_done = 0.0;
+    int launch_idx = 0;
+    for (int first = 0; first < count; ++launch_idx) {
+        int n_here = 0;
+        const double target = total_work * (double)(launch_idx + 1) / (double)n_launches;
+        const int remaining_launches = n_launches - launch_idx - 1;
+        while (first + n_here < count && n_here < kMaxGroup) {
+            const GroupedLinear &q = problems[first + n_here];
+            const double w = (double)((q.n + 255) / 256) * (double)((q.k + BK - 1) / BK);
+            // stop at the work target unless the launches that follow could not hold what would be left
+            const bool rest_fits = (long long)(count - first - n_here) <= (long long)remaining_launches * kMaxGroup;
+            if (n_here > 0 && work_done + 0.5 * w > target && rest_fits) break;
+            work_done += w;
+            ++n_here;
+        }
         gp.count = n_here; gp.act = act; gp.out_dtype = out_dtype;
         gp.status = status_slot(true);
         gp.wait_limit_ns = wait_limit_ns();
+        gp.static_weights = static_weights;
         gp.w_kx = w_layout == B200_W_SLAB128 ? 0 : BK;
         gp.w_kz = w_layout == B200_W_SLAB128 ? 1 : 0;
         int tiles = 0;
@@ -1359,9 +1407,10 @@ int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int a
             const int a_rows = ((q.m + 15) / 16) * 16;
             GroupedProblem &d = gp.prob[i];
             d.row_scales = q.row_scales; d.col_scales = q.col_scales; d.bias = q.bias;
-            d.residual = q.residual; d.out = q.out; d.ldo = q.ldo; d.ldr = q.ldr;
-            d.m = q.m; d.n = q.n; d.k_blocks = (q.k + BK - 1) / BK;
-            d.a_bytes = a_rows * BK;
+            if (q.ldo > 0x7fffffffLL || q.ldr > 0x7fffffffLL || (q.k + BK - 1) / BK > 0xffff)
+                return fail("linear_grouped: problem %d: row strides must be below 2^31 elements and K below 8 388 480", first + i);
+            d.residual = q.residual; d.out = q.out; d.ldo = (int)q.ldo; d.ldr = (int)q.ldr;
+            d.m = q.m; d.n = q.n; d.k_blocks = (unsigned short)((q.k + BK - 1) / BK);
             d.tile0 = tiles;
             d.vec_ok = (!q.residual || (aligned16(q.residual) && ((q.ldr * esz) % 16 == 0))) && aligned16(q.col_scales) &&
                        (!q.bias || aligned16(q.bias));
@@ -1386,6 +1435,7 @@ int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int a
         else le = launch_kernel(gemm_i8_grouped_kernel<B200_DT_BF16>, dim3(grid), dim3(kThreads), (size_t)C::kSmemBytes, stream, gp);
         if (le != cudaSuccess) return fail("launching gemm_i8_grouped: %s", cudaGetErrorString(le));
         if (check_launch("gemm_i8_grouped")) return 1;
+        first += n_here;
     }
     return 0;
 }

@@ -148,7 +148,7 @@ struct GroupedLinear {
     int m, k, n;
 };
 int linear_grouped(const GroupedLinear *problems, int count, int w_layout, int act, int out_dtype,
-                   cudaStream_t stream);
+                   cudaStream_t stream, int static_weights = 0);
 int gemm_can_implement(const LinearArgs &a, bool verbose);
 int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemm_workspace_size(int m, int k, int n);
