@@ -170,3 +170,27 @@ def test_config4_all_shapes_in_one_grouped_launch(pkg, ref):
     assert pkg.poll_status() == 0
     for y, want in zip(outs, wants):
         assert same(y, want)
+
+
+def test_config4_seventy_two_small_weight_linears_in_one_grouped_launch(pkg, ref):
+    """The grouped call bench.py times on the 4 MB weights: 72 distinct 2048 -> 2048 linears at M=16 in one
+    launch, each equal to the same linear launched alone and, for a sample, to the oracle."""
+    m, k, n = 16, 2048, 2048
+    g = torch.Generator().manual_seed(4242)
+    qx, sx = ref.quantize_rows(torch.randn(m, k, generator=g))
+    probs, hosts = [], []
+    for i in range(72):
+        qw = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+        sw = torch.rand(n, generator=g) * 2e-4 + 1e-5
+        packed = qw.view(n, k // 128, 128).permute(1, 0, 2).contiguous()
+        probs.append(dict(x_i8=qx.to(DEV), x_scales=sx.to(DEV), w_i8=packed.to(DEV), w_scales=sw.to(DEV), n=n))
+        hosts.append((qw, sw))
+    outs = pkg.linear_grouped(probs, w_layout=pkg.W_SLAB128, out_dtype=torch.float16, const_weights=True)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    for i, (q, y) in enumerate(zip(probs, outs)):
+        single = pkg.linear(q["x_i8"], q["x_scales"], q["w_i8"], q["w_scales"], n=n, w_layout=pkg.W_SLAB128,
+                            out_dtype=torch.float16)
+        assert same(y, single)
+        if i % 24 == 0:
+            assert same(y, ref.linear_w8a8(qx, sx, *hosts[i], out_dtype=torch.float16))

@@ -108,7 +108,7 @@ def test_dequant_act_quantize_rows(pkg, ref, parity_log, act, rows, cols, with_b
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("rows,cols", [(512, 2048), (33, 100), (70000, 8)])
+@pytest.mark.parametrize("rows,cols", [(512, 2048), (33, 100), (70000, 8), (16384, 2048)])
 @pytest.mark.parametrize("gated", [False, True])
 def test_dequant_residual_bit_exact(pkg, ref, dtype, rows, cols, gated):
     g = torch.Generator().manual_seed(rows)

@@ -478,7 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             ++t;
         }
         // the staging block must outlive the bulk store that reads it
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncwarp();
     }
 

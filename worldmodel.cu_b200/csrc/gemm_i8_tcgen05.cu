@@ -555,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (warp == 2 && lane == 0) trace_mark(p, 5);
         }
         // the staging blocks must outlive the bulk stores that read them
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncwarp();
     }
 
@@ -977,7 +977,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
             if (lane == 0) mbar_arrive(&bar_tempty[b]);
         }
         // the staging blocks must outlive the bulk stores that read them
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncwarp();
     }
 
