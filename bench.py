@@ -471,6 +471,8 @@ def main():
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers of the stack (24 = the real workload)")
     ap.add_argument("--band", type=int, default=-1, help="rows per band (default: the workload's own)")
     ap.add_argument("--lanes", type=int, default=0, help="streams that bands alternate over (default 2 for cfg3)")
+    ap.add_argument("--pair-mma", type=int, default=0, choices=[0, 1, 2],
+                    help="CTA-pair (cta_group::2) GEMM: 0 = the planner decides, 1 = wherever legal, 2 = never")
     ap.add_argument("--fusion", action="store_true",
                     help="let the linears with d_model outputs emit the next linear's codes from their epilogue "
                          "(six launches per layer instead of ten; measured slower, off by default)")
@@ -502,7 +504,7 @@ def main():
         return float(t.item())
 
     pkg, ref = load_package(), load_oracle()
-    pkg.lib()  # raises if the CUDA library is missing
+    pkg.lib().b200_w8a8_set_pair_mma(args.pair_mma)  # (lib() raises if the CUDA library is missing)
     peaks = measured_peaks()
     rows, chained, dt_name, band = WORKLOADS[args.workload]
     sharding = _load("w8a8_sharding", ROOT / "worldmodel.cu_b200" / "sharding.py")

@@ -311,8 +311,11 @@ int b200_w8a8_stack_set_layer(void *stack, int layer, const float *w_qkv, const 
  * the pass once per (x_dev, y_dev, rows, steps) and replays it; it needs a real stream. */
 int b200_w8a8_stack_forward(void *stack, const void *x_dev, void *y_dev, int rows, int steps, int use_graph,
                             void *stream);
-/* Same with HOST buffers (pinned for full speed): copies in, runs, copies out, and
- * returns after the result has landed. */
+/* Same with HOST buffers (pinned for full speed; use_graph = 1 bakes the two host pointers into the
+ * captured graph): every band of rows is copied in, run through all layers and copied out as a
+ * pipeline over two copy streams and the lanes, so the transfers of one band run under the kernels of
+ * the others; returns after the whole result has landed.  The reference's runtime has the same shape at
+ * its own boundary: host RGB out at the end of a step (src/world_cuda.cu:2376-2383). */
 int b200_w8a8_stack_forward_host(void *stack, const void *x_host, void *y_host, int rows, int steps, int use_graph);
 /* lanes = 2 runs alternate bands of rows on two streams (a second scratch set is allocated once),
  * so the bandwidth-bound quantizers of one band overlap the tensor-bound GEMMs of the other.

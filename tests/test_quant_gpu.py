@@ -163,3 +163,22 @@ def test_quantize_rows_many_scales_bit_exact(pkg, ref):
     q, s = pkg.quantize_rows(x.to(DEV))
     assert torch.equal(bits(s), bits(s_ref))
     assert torch.equal(q.cpu(), q_ref)
+
+
+def test_qkv_consumer_refuses_a_misaligned_accumulator(pkg):
+    """The stand-alone QKV consumer reads accumulators and weight scales two at a time: a view that starts on an odd
+    element must come back as an error (return 1 + message), not as a misaligned access on the device."""
+    T, Hq, Hkv, d = 8, 2, 1, 64
+    n = (Hq + 2 * Hkv) * d
+    acc = torch.zeros(T * n + 1, dtype=torch.int32, device=DEV)[1:].view(T, n)   # 4-byte offset
+    sa, sw = torch.ones(T, device=DEV), torch.ones(n, device=DEV)
+    pos = torch.zeros(T, dtype=torch.int64, device=DEV)
+    xy, inv_t = torch.ones(d // 8, device=DEV), torch.ones(d // 2 - 2 * (d // 8), device=DEV)
+    with pytest.raises(pkg.W8A8Error, match="8-byte aligned"):
+        pkg.qkv_rms_rope_dequant(acc, sa, sw, pos, pos, pos, xy, inv_t, Hq, Hkv, d, 16, 8, 1e-6)
+
+
+def test_mma_rate_self_test_reports_a_plausible_ceiling(pkg):
+    rate = pkg.mma_rate(4096)
+    assert 1000.0 < rate < 9000.0, rate   # TOP/s: above any GEMM of this library, below twice the nominal dense figure
+    assert pkg.poll_status() == 0

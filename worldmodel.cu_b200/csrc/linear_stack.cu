@@ -60,6 +60,11 @@ struct Stack {
     bool fuse_ok = false;  // the shapes allow it (d_model a multiple of 256, at most 2048)
     cudaStream_t lane_stream = nullptr;   // stream of the second lane
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    // host entry point: bands are copied in, computed and copied out as a pipeline
+    cudaStream_t copy_in_stream = nullptr, copy_out_stream = nullptr;
+    cudaEvent_t ev_copy_fork = nullptr, ev_copy_join = nullptr;
+    std::vector<cudaEvent_t> ev_band_in, ev_band_done;
+    std::map<std::tuple<const void *, void *, int, int>, cudaGraphExec_t> host_graphs;
     void *host_stage = nullptr; // device staging for the host entry point
     void *host_out = nullptr;
     cudaStream_t own_stream = nullptr;
@@ -182,16 +187,57 @@ int layer_band(Stack *s, const Stack::Scratch &w, const Layer &L, const void *x,
     return 0;
 }
 
-int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t st) {
+// Streams and events of the copy pipeline of the host entry point, created on first use.
+int ensure_copy_pipeline(Stack *s, int n_bands) {
+    if (!s->copy_in_stream) {
+        if (cudaStreamCreateWithFlags(&s->copy_in_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaStreamCreateWithFlags(&s->copy_out_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->ev_copy_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->ev_copy_join, cudaEventDisableTiming) != cudaSuccess)
+            return fail("creating the copy streams failed");
+    }
+    while ((int)s->ev_band_in.size() < n_bands) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        if (cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess)
+            return fail("creating the band events failed");
+        s->ev_band_in.push_back(a);
+        s->ev_band_done.push_back(b);
+    }
+    return 0;
+}
+
+// Enqueues `steps` passes over `rows` rows.  With x_host / y_host given (the host entry point) every band's
+// rows are copied in on a copy stream before that band's kernels and copied out on another after them, so
+// that the transfers of one band run under the kernels of the others; x and y are then device staging.
+int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t st, const void *x_host = nullptr,
+            void *y_host = nullptr) {
     const size_t row_bytes = (size_t)s->d * esize(s->dtype);
     const int total_layers = steps * s->n_layers;
     long long launches = 0;
     const int n_bands = (rows + s->band_rows - 1) / s->band_rows;
     const bool two_lanes = s->lanes == 2 && n_bands >= 2;
+    const bool piped = x_host != nullptr;
     if (two_lanes) {  // the second lane starts after everything already queued on the caller's stream
         if (cudaEventRecord(s->ev_fork, st) != cudaSuccess ||
             cudaStreamWaitEvent(s->lane_stream, s->ev_fork, 0) != cudaSuccess)
             return fail("forking the second lane failed");
+    }
+    if (piped) {
+        if (ensure_copy_pipeline(s, n_bands)) return 1;
+        if (cudaEventRecord(s->ev_copy_fork, st) != cudaSuccess ||
+            cudaStreamWaitEvent(s->copy_in_stream, s->ev_copy_fork, 0) != cudaSuccess ||
+            cudaStreamWaitEvent(s->copy_out_stream, s->ev_copy_fork, 0) != cudaSuccess)
+            return fail("forking the copy streams failed");
+        int b = 0;
+        for (int r0 = 0; r0 < rows; r0 += s->band_rows, ++b) {
+            const int nr = rows - r0 < s->band_rows ? rows - r0 : s->band_rows;
+            const size_t off = (size_t)r0 * row_bytes;
+            if (cudaMemcpyAsync((char *)const_cast<void *>(x) + off, (const char *)x_host + off, (size_t)nr * row_bytes,
+                                cudaMemcpyHostToDevice, s->copy_in_stream) != cudaSuccess ||
+                cudaEventRecord(s->ev_band_in[b], s->copy_in_stream) != cudaSuccess)
+                return fail("queueing the H2D copy of band %d failed", b);
+        }
     }
     int band = 0;
     for (int r0 = 0; r0 < rows; r0 += s->band_rows, ++band) {
@@ -200,6 +246,8 @@ int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t 
         cudaStream_t bst = lane ? s->lane_stream : st;
         const Stack::Scratch &w = s->scratch[lane];
         const size_t off = (size_t)r0 * row_bytes;
+        if (piped && cudaStreamWaitEvent(bst, s->ev_band_in[band], 0) != cudaSuccess)
+            return fail("waiting for the H2D copy of band %d failed", band);
         const void *cur = (const char *)x + off;
         int cur_slot = -1;  // -1: caller's input
         const bool fuse = s->fusion && s->fuse_ok;
@@ -227,6 +275,18 @@ int enqueue(Stack *s, const void *x, void *y, int rows, int steps, cudaStream_t 
             cur = x3;
             cur_slot = x3_slot;
         }
+        if (piped) {
+            if (cudaEventRecord(s->ev_band_done[band], bst) != cudaSuccess ||
+                cudaStreamWaitEvent(s->copy_out_stream, s->ev_band_done[band], 0) != cudaSuccess ||
+                cudaMemcpyAsync((char *)y_host + off, (const char *)y + off, (size_t)nr * row_bytes, cudaMemcpyDeviceToHost,
+                                s->copy_out_stream) != cudaSuccess)
+                return fail("queueing the D2H copy of band %d failed", band);
+        }
+    }
+    if (piped) {  // every copy stream rejoins the caller's stream (the copy-in stream through the lanes that waited on it)
+        if (cudaEventRecord(s->ev_copy_join, s->copy_out_stream) != cudaSuccess ||
+            cudaStreamWaitEvent(st, s->ev_copy_join, 0) != cudaSuccess)
+            return fail("joining the copy streams failed");
     }
     if (two_lanes) {  // the caller's stream continues only when the second lane is done
         if (cudaEventRecord(s->ev_join, s->lane_stream) != cudaSuccess ||
@@ -293,6 +353,13 @@ void b200_w8a8_stack_destroy(void *handle) {
     Stack *s = reinterpret_cast<Stack *>(handle);
     if (!s) return;
     for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);
+    for (auto &kv : s->host_graphs) cudaGraphExecDestroy(kv.second);
+    for (cudaEvent_t e : s->ev_band_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : s->ev_band_done) cudaEventDestroy(e);
+    if (s->copy_in_stream) cudaStreamDestroy(s->copy_in_stream);
+    if (s->copy_out_stream) cudaStreamDestroy(s->copy_out_stream);
+    if (s->ev_copy_fork) cudaEventDestroy(s->ev_copy_fork);
+    if (s->ev_copy_join) cudaEventDestroy(s->ev_copy_join);
     for (auto &L : s->layers) {
         Weight *ws[5] = {&L.qkv, &L.out, &L.ctrl, &L.up, &L.down};
         for (Weight *w : ws) {
@@ -438,6 +505,8 @@ int b200_w8a8_stack_set_lanes(void *handle, int lanes) {
     if (lanes != s->lanes) {
         for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);
         s->graphs.clear();
+        for (auto &kv : s->host_graphs) cudaGraphExecDestroy(kv.second);
+        s->host_graphs.clear();
         s->lanes = lanes;
     }
     return 0;
@@ -449,6 +518,8 @@ int b200_w8a8_stack_set_fusion(void *handle, int on) {
     if ((on != 0) != (s->fusion != 0)) {
         for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);
         s->graphs.clear();
+        for (auto &kv : s->host_graphs) cudaGraphExecDestroy(kv.second);
+        s->host_graphs.clear();
         s->fusion = on != 0;
     }
     return 0;
@@ -460,6 +531,8 @@ int b200_w8a8_stack_set_act_dtype(void *handle, int act_dtype) {
     if (act_dtype != s->dtype) {
         for (auto &kv : s->graphs) cudaGraphExecDestroy(kv.second);  // captured launches bake the type in
         s->graphs.clear();
+        for (auto &kv : s->host_graphs) cudaGraphExecDestroy(kv.second);
+        s->host_graphs.clear();
         s->dtype = act_dtype;
     }
     return 0;
@@ -513,15 +586,42 @@ int b200_w8a8_stack_forward(void *handle, const void *x_dev, void *y_dev, int ro
 
 int b200_w8a8_stack_forward_host(void *handle, const void *x_host, void *y_host, int rows, int steps, int use_graph) {
     Stack *s = reinterpret_cast<Stack *>(handle);
+    if (status_check_entry()) return 1;
     if (!s || !x_host || !y_host || rows <= 0 || rows > s->max_rows || steps <= 0)
         return fail("invalid stack_forward_host arguments rows=%d steps=%d", rows, steps);
-    const size_t bytes = (size_t)rows * s->d * esize(s->dtype);
-    cudaError_t e = cudaMemcpyAsync(s->host_stage, x_host, bytes, cudaMemcpyHostToDevice, s->own_stream);
-    if (e != cudaSuccess) return fail("H2D copy: %s", cudaGetErrorString(e));
-    if (b200_w8a8_stack_forward(s, s->host_stage, s->host_out, rows, steps, use_graph, s->own_stream)) return 1;
-    e = cudaMemcpyAsync(y_host, s->host_out, bytes, cudaMemcpyDeviceToHost, s->own_stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s->own_stream);
-    if (e != cudaSuccess) return fail("D2H copy / synchronize: %s", cudaGetErrorString(e));
+    for (const Layer &L : s->layers)
+        if (!L.loaded) return fail("stack_forward_host called before every layer was loaded");
+    cudaStream_t st = s->own_stream;
+    cudaError_t e = cudaSuccess;
+    if (!use_graph) {
+        if (enqueue(s, s->host_stage, s->host_out, rows, steps, st, x_host, y_host)) return 1;
+    } else {
+        // copies and kernels of all bands as one graph: the host pointers are part of the key
+        auto key = std::make_tuple(x_host, y_host, rows, steps);
+        auto it = s->host_graphs.find(key);
+        if (it == s->host_graphs.end()) {
+            const int n_bands = (rows + s->band_rows - 1) / s->band_rows;
+            if (ensure_copy_pipeline(s, n_bands)) return 1;  // nothing is created while the capture runs
+            cudaGraph_t graph = nullptr;
+            e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+            if (e != cudaSuccess) return fail("cudaStreamBeginCapture: %s", cudaGetErrorString(e));
+            const int rc = enqueue(s, s->host_stage, s->host_out, rows, steps, st, x_host, y_host);
+            e = cudaStreamEndCapture(st, &graph);
+            if (rc || e != cudaSuccess || !graph) {
+                if (graph) cudaGraphDestroy(graph);
+                return rc ? 1 : fail("cudaStreamEndCapture: %s", cudaGetErrorString(e));
+            }
+            cudaGraphExec_t exec = nullptr;
+            e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) return fail("cudaGraphInstantiate: %s", cudaGetErrorString(e));
+            it = s->host_graphs.emplace(key, exec).first;
+        }
+        e = cudaGraphLaunch(it->second, st);
+        if (e != cudaSuccess) return fail("cudaGraphLaunch: %s", cudaGetErrorString(e));
+    }
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail("synchronizing the host entry point: %s", cudaGetErrorString(e));
     return 0;
 }
 
