@@ -60,22 +60,23 @@ def golden():
 
 @pytest.fixture(scope="session")
 def parity_log():
-    """record(name, mismatches, positions): prints a measured mismatch count and, when the run has a
-    scratch output folder, appends it to gpurun_out/parity_counts.jsonl so the numbers quoted in the
-    design notes can be refreshed from a test run."""
+    """record(name, mismatches, positions): prints a measured mismatch count and, when the environment variable
+    W8A8_PARITY_LOG names a file, appends it there as a JSON line, so the numbers quoted in the design notes can
+    be refreshed from a test run."""
     import json
+    import os
 
     def record(name, mismatches, positions, **extra):
         row = dict(name=name, mismatches=int(mismatches), positions=int(positions),
                    rate=float(mismatches) / max(int(positions), 1), **extra)
         print("PARITY", json.dumps(row))
-        out = ROOT / "gpurun_out"
-        try:
-            out.mkdir(exist_ok=True)
-            with open(out / "parity_counts.jsonl", "a") as f:
-                f.write(json.dumps(row) + "\n")
-        except OSError:
-            pass
+        path = os.environ.get("W8A8_PARITY_LOG")
+        if path:
+            try:
+                with open(path, "a") as f:
+                    f.write(json.dumps(row) + "\n")
+            except OSError:
+                pass
         return row
 
     return record
