@@ -134,6 +134,10 @@ void b200_w8a8_set_tile_width(int bn);
  * cluster) for every later launch; (0, 0, 0) restores the planner.  Not thread-safe by design: set it
  * from the only thread that launches. */
 void b200_w8a8_debug_force_plan(int tile_width, int k_splits, int split_mode);
+/* Tuning aid: 64-wide tiles of an unsplit launch normally bring two 128-byte K slabs per copy and pipeline
+ * stage (the copy engine's cost is per copy, not per byte); on = 1 keeps one slab per stage everywhere, for
+ * A/B timing.  Results are identical either way. */
+void b200_w8a8_debug_one_slab_stages(int on);
 /* Tuning aid: 0 = the planner decides when two CTAs share one 256 x 256 tile (cta_group::2 MMA),
  * 1 = whenever the launch allows it (M > 128, unsplit 256-wide tiles, aligned buffers,
  * N % 32 == 0), 2 = never.  No counterpart in the reference. */

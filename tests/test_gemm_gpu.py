@@ -238,3 +238,33 @@ def test_pair_mma_gemm_bit_exact(pkg, ref, pair_mma, m, k, n):
                      bias=bias.to(DEV), residual=res.to(DEV), out_dtype=torch.float16)
     assert pkg.poll_status() == 0
     assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("m,k,n", [(512, 2048, 2048), (100, 512, 520), (16, 2048, 2048), (300, 256, 64), (640, 8192, 2048)])
+@pytest.mark.parametrize("use_slab", [False, True])
+def test_two_slab_stages_of_narrow_tiles_bit_exact(pkg, ref, m, k, n, use_slab):
+    """64-wide tiles of an unsplit launch bring two K slabs per copy and pipeline stage.  Forced to that tile width,
+    with and without the two-slab stages, the accumulators and a fused fp16 linear must equal the oracle."""
+    a, b = codes(m, k, m + 1), codes(n, k, n + 2)
+    g = torch.Generator().manual_seed(m + n)
+    sx = torch.rand(m, generator=g) * 0.05 + 0.01
+    sw = torch.rand(n, generator=g) * 2e-4 + 1e-5
+    res = torch.randn(m, n, generator=g).half()
+    want_acc = ref.gemm_i8_i32(a, b)
+    want = ref.linear_w8a8(a, sx, b, sw, residual=res, out_dtype=torch.float16)
+    wd = (slab(b) if use_slab else b).to(DEV)
+    layout = pkg.W_SLAB128 if use_slab else pkg.W_ROW_MAJOR
+    lib = pkg.lib()
+    lib.b200_w8a8_debug_force_plan(64, 1, 0)
+    try:
+        for one_slab in (0, 1):
+            lib.b200_w8a8_debug_one_slab_stages(one_slab)
+            acc = pkg.gemm_i8_i32(a.to(DEV), wd, n=n, w_layout=layout)
+            y = pkg.linear(a.to(DEV), sx.to(DEV), wd, sw.to(DEV), n=n, w_layout=layout, residual=res.to(DEV),
+                           out_dtype=torch.float16)
+            assert pkg.poll_status() == 0
+            assert torch.equal(acc.cpu(), want_acc), f"accumulators differ (one_slab={one_slab})"
+            assert torch.equal(y.cpu(), want), f"fused linear differs (one_slab={one_slab})"
+    finally:
+        lib.b200_w8a8_debug_one_slab_stages(0)
+        lib.b200_w8a8_debug_force_plan(0, 0, 0)

@@ -51,6 +51,7 @@ _PROTOTYPES = {
     "b200_w8a8_debug_set_wait_limit_ns": (None, [ctypes.c_ulonglong]),
     "b200_w8a8_debug_drop_operand_load": (None, [c_int]),
     "b200_w8a8_debug_force_plan": (None, [c_int, c_int, c_int]),
+    "b200_w8a8_debug_one_slab_stages": (None, [c_int]),
     "b200_w8a8_linear_requant": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,
                                          c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int64, c_void_p,

@@ -153,6 +153,7 @@ int b200_w8a8_gemm_i8_i32(const int8_t *x_i8, const int8_t *w_i8, int w_layout, 
 
 void b200_w8a8_set_tile_width(int bn) { gemm_set_tile_width(bn); }
 void b200_w8a8_set_pair_mma(int mode) { gemm_set_pair_mode(mode); }
+void b200_w8a8_debug_one_slab_stages(int on) { gemm_set_one_slab_stages(on); }
 void b200_w8a8_set_overlapped_launch(int on) { set_pdl_enabled(on != 0); }
 void b200_w8a8_set_trace_buffer(void *dev_buf) { gemm_set_trace_buffer(reinterpret_cast<unsigned long long *>(dev_buf)); }
 

@@ -49,6 +49,8 @@ struct GemmParams {
     int32_t *ws_partials;                // [splits][M][N] raw partial accumulators (split-K only)
     int *ws_counters;                    // [tiles] arrival tickets, zero between launches
     int b_kx, b_kz;  // W coordinate multipliers: row-major (128,0), slab layout (0,1)
+    int a_kx, a_kz;  // the same for A: row-major (128,0), slab-by-slab view (0,1)
+    int slabs_per_stage;  // K slabs one copy brings and one pipeline stage holds (1 or 2)
     const float *row_scales;
     const float *col_scales;
     const float *bias;
@@ -371,12 +373,12 @@ EncodeTiledFn encode_fn() {
 
 // A byte matrix seen as (inner 128-byte run, rows, slabs) with the 128-byte swizzle.
 int make_map(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1,
-             uint64_t stride2, uint32_t box_rows) {
+             uint64_t stride2, uint32_t box_rows, uint32_t box_depth = 1) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail("cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[3] = {d0, d1, d2};
     cuuint64_t strides[2] = {stride1, stride2};
-    cuuint32_t box[3] = {BK, box_rows, 1};
+    cuuint32_t box[3] = {BK, box_rows, box_depth};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -181,6 +181,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // Slabs of K per pipeline stage: 1, or 2 for narrow tiles, where the copy engine's cost per copy (not per
+    // byte) bounds the main loop: one copy then brings two 128-byte slabs of A (or of W), the ring has half as
+    // many stages of twice the size, and a stage feeds eight MMAs instead of four.
+    const int kd = p.slabs_per_stage;
+    const int n_stages = C::kStages / kd;
+    const int stage_bytes = kd * C::kStageBytes;
+    const int b_off = kd * C::kABytes;  // the W slabs of a stage follow its A slabs
 
     pdl_trigger();  // the next kernel of the stream may be scheduled from here on
     if (threadIdx.x == 0) {
@@ -221,12 +228,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (p.static_weights && blockIdx.x < p.num_work) {
                 int tile, m_blk, n_blk, kb0, kb1;
                 decode_work(p, blockIdx.x, tile, m_blk, n_blk, kb0, kb1);
-                prefetched = min(kb1 - kb0, C::kStages);
+                prefetched = min((kb1 - kb0) / kd, n_stages);
                 for (int i = 0; i < prefetched; ++i) {
-                    uint8_t *sa = smem + i * C::kStageBytes;
-                    mbar_arrive_expect_tx(&bar_full[i], (uint32_t)(p.a_stage_bytes + C::kBBytes));
-                    tma_load_3d(sa + C::kABytes, &tm_b, &bar_full[i], (kb0 + i) * p.b_kx, n_blk * BN,
-                                (kb0 + i) * p.b_kz);
+                    uint8_t *sa = smem + i * stage_bytes;
+                    mbar_arrive_expect_tx(&bar_full[i], (uint32_t)(kd * (p.a_stage_bytes + C::kBBytes)));
+                    tma_load_3d(sa + b_off, &tm_b, &bar_full[i], (kb0 + i * kd) * p.b_kx, n_blk * BN,
+                                (kb0 + i * kd) * p.b_kz);
                 }
             }
             pdl_wait();
@@ -234,23 +241,23 @@ __global__ void __launch_bounds__(kThreads, 1)
                 int tile, m_blk, n_blk, kb0, kb1;
                 decode_work(p, work, tile, m_blk, n_blk, kb0, kb1);
                 const int m0 = m_blk * BM, n0 = n_blk * BN;
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    uint8_t *sa = smem + s * C::kStageBytes;
+                for (int kb = kb0; kb < kb1; kb += kd) {
+                    uint8_t *sa = smem + s * stage_bytes;
                     // test aid: leaving out the very first A tile makes the MMA issuer's wait run out
                     const bool drop = p.debug_drop_a_load && work == (int)blockIdx.x && kb == kb0;
                     if (prefetched > 0) {
                         // stage already armed and its W tile already requested
                         --prefetched;
-                        if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
+                        if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * p.a_kx, m0, kb * p.a_kz);
                     } else {
                         ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx,
                                                KS_TIMEOUT_SMEM_EMPTY);
                         if (!ok) break;
-                        mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(p.a_stage_bytes + C::kBBytes));
-                        if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m0, 0);
-                        tma_load_3d(sa + C::kABytes, &tm_b, &bar_full[s], kb * p.b_kx, n0, kb * p.b_kz);
+                        mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(kd * (p.a_stage_bytes + C::kBBytes)));
+                        if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * p.a_kx, m0, kb * p.a_kz);
+                        tma_load_3d(sa + b_off, &tm_b, &bar_full[s], kb * p.b_kx, n0, kb * p.b_kz);
                     }
-                    if (++s == C::kStages) { s = 0; ph ^= 1u; }
+                    if (++s == n_stages) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -275,20 +282,22 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = kb0; kb < kb1; kb += kd) {
                     ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     if (t == 0 && kb == kb0) trace_mark(p, 2);
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_u32(smem + s * C::kStageBytes);
-                    const uint64_t da = umma_smem_desc_k128(sa);
-                    const uint64_t db = umma_smem_desc_k128(sa + C::kABytes);
+                    const uint32_t sa = smem_u32(smem + s * stage_bytes);
+                    for (int d = 0; d < kd; ++d) {
+                        const uint64_t da = umma_smem_desc_k128(sa + (uint32_t)(d * p.a_stage_bytes));
+                        const uint64_t db = umma_smem_desc_k128(sa + (uint32_t)(b_off + d * C::kBBytes));
 #pragma unroll
-                    for (int j = 0; j < BK / 32; ++j)
-                        umma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc,
-                                (uint32_t)(((kb - kb0) | j) != 0));
+                        for (int j = 0; j < BK / 32; ++j)
+                            umma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc,
+                                    (uint32_t)(((kb - kb0) | d | j) != 0));
+                    }
                     umma_commit(&bar_empty[s]);
-                    if (++s == C::kStages) { s = 0; ph ^= 1u; }
+                    if (++s == n_stages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit(&bar_tfull[b]);
                 trace_mark(p, 3);
@@ -995,6 +1004,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_i8_grouped_kernel(const __gr
 }
 
 
+std::atomic<int> g_one_slab_stages{0};  // tuning: 1 = never put two K slabs into one pipeline stage
+
 template <int BN, int OUT, bool GENERAL, int SPLITK>
 int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t stream) {
     using C = Cfg<BN, OUT == kOutQkvHeads>;
@@ -1017,13 +1028,31 @@ int launch_bn_g(const LinearArgs &a, GemmParams &p, int slot, cudaStream_t strea
     // lanes beyond M multiply whatever the stage held before and are never read back)
     const int a_rows = a.m >= BM ? BM : ((a.m + 15) / 16) * 16;
     p.a_stage_bytes = a_rows * BK;
+    // Two K slabs per stage for the narrowest tiles of an unsplit launch with an even number of slabs: the
+    // operands are then described slab by slab ({128 bytes, rows, K/128}) and one copy takes a box two slabs deep.
+    const bool two_slabs = BN == 64 && SPLITK == 0 && OUT != kOutQkvHeads && p.splits <= 1 && a.k % (2 * BK) == 0 &&
+                           !g_one_slab_stages;
+    p.slabs_per_stage = two_slabs ? 2 : 1;
 
     CUtensorMap tm_a, tm_b;
-    if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m,
-                 (uint32_t)a_rows))
-        return 1;
+    if (two_slabs) {
+        if (make_map(&tm_a, a.x, BK, (uint64_t)a.m, (uint64_t)(a.k / BK), (uint64_t)a.k, BK, (uint32_t)a_rows, 2)) return 1;
+        p.a_kx = 0;
+        p.a_kz = 1;
+    } else {
+        if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m,
+                     (uint32_t)a_rows))
+            return 1;
+        p.a_kx = BK;
+        p.a_kz = 0;
+    }
     if (a.w_layout == B200_W_SLAB128) {
-        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, BN)) return 1;
+        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, BN, two_slabs ? 2 : 1))
+            return 1;
+        p.b_kx = 0;
+        p.b_kz = 1;
+    } else if (two_slabs) {
+        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), (uint64_t)a.k, BK, BN, 2)) return 1;
         p.b_kx = 0;
         p.b_kz = 1;
     } else {
@@ -1112,6 +1141,7 @@ void gemm_force_plan(int bn, int splits, int mode) {
     g_force_mode = mode;
 }
 void gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
+void gemm_set_one_slab_stages(int on) { g_one_slab_stages = on != 0; }
 void gemm_set_trace_buffer(unsigned long long *dev_buf) { g_trace = dev_buf; }
 unsigned long long *gemm_trace_buffer() { return g_trace; }
 

@@ -170,6 +170,7 @@ int linear_static_scratch(const LinearArgs &a, cudaStream_t stream);
 size_t static_scratch_capacity();
 void gemm_set_tile_width(int bn);
 void gemm_set_pair_mode(int mode);
+void gemm_set_one_slab_stages(int on);
 void gemm_set_trace_buffer(unsigned long long *dev_buf);
 unsigned long long *gemm_trace_buffer();
 void gemm_force_plan(int bn, int splits, int mode);
