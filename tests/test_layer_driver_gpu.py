@@ -192,3 +192,27 @@ def test_layer_driver_against_the_reference_operators_on_the_same_gpu(pkg, parit
     # fast-math quantizer of the reference put a code one step away); bounds are twice the measured values
     assert float(err.max()) <= 1.1e-2 * std and row["rate"] < 2.7e-3
     drv.close()
+
+
+def test_layer_driver_without_modulation_vectors_or_conditioning(pkg):
+    """mod_scale / mod_bias / ctrl_cond are nullable (plain RMSNorm, no bias before the controller's SiLU)."""
+    T, D, HQ, HKV, DH, HID, W, H, eps = 64, 256, 4, 2, 64, 512, 16, 6, 1e-6
+    host = make_layer(D, HQ, HKV, DH, HID, 31)
+    for key in ("mod_scale0", "mod_bias0", "ctrl_cond", "mod_scale1", "mod_bias1"):
+        del host[key]
+    L = {k: v.to(DEV) for k, v in host.items()}
+    g = torch.Generator().manual_seed(12)
+    tokens = torch.randn(T, D, generator=g).to(DEV)
+    attn = torch.randn(T, D, generator=g).to(DEV)
+    pos, xy, inv_t = frame(T, DH, W, H, 2)
+    cos, sin = pkg.rope_tables(*[p.to(DEV) for p in pos], xy.to(DEV), inv_t.to(DEV), DH, W, H)
+    drv = pkg.ReferenceLayerDriver(T, D, HQ, HKV, DH, HID, eps)
+    q, k, v = drv.qkv(L, tokens, cos, sin)
+    nxt = drv.after_attention(L, attn, tokens)
+    full = dict(L, mod_scale0=None, mod_bias0=None, mod_scale1=None, mod_bias1=None)
+    (qc, kc, vc), want = composition(pkg, full, tokens, attn, cos, sin, HQ, HKV, DH, eps, pkg.W_ROW_MAJOR)
+    torch.cuda.synchronize()
+    assert torch.equal(q, qc) and torch.equal(k, kc) and torch.equal(v, vc) and torch.equal(nxt, want)
+    with pytest.raises(pkg.W8A8Error, match="invalid layer_after_attention"):
+        drv.after_attention(dict(L, gate1=None), attn, tokens)
+    drv.close()

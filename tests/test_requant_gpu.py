@@ -109,3 +109,25 @@ def test_linear_requant_rejects_unsupported_width(pkg):
     sw = torch.ones(384, device=dev)
     with pytest.raises(pkg.W8A8Error, match="q_cols"):
         pkg.linear_requant(qx, sx, w, sw, n=384, w_layout=pkg.W_SLAB128, q_cols=384)
+
+
+@pytest.mark.parametrize("m,k,n,q_cols", [(16, 512, 2304, 2048), (200, 256, 1312, 1024), (129, 1024, 512, 512)])
+def test_linear_requant_modulation_form_ragged_groups_and_short_row_blocks(pkg, m, k, n, q_cols):
+    """(1 + modulation) scale with a bias (the reference's AdaRMSNorm form), a last column group that is not a whole
+    cluster of tiles (N is no multiple of q_cols or of 256), and row counts that leave a row block mostly empty."""
+    dev = "cuda"
+    x, w, res, gamma, nbias, bias, gate = _inputs(m, k, n, 77 + m, torch.float32)
+    qx, sx = pkg.quantize_rows(x.to(dev))
+    packed, sw = pkg.pack_weight(w, layout=pkg.W_SLAB128)
+    packed, sw, resd = packed.to(dev), sw.to(dev), res.to(dev)
+    mod = (gamma - 1.0)[:q_cols].to(dev)
+    nb = nbias[:q_cols].to(dev)
+    y2 = pkg.linear(qx, sx, packed, sw, n=n, w_layout=pkg.W_SLAB128, gate=gate.to(dev), residual=resd,
+                    out_dtype=torch.float32)
+    q2, s2 = pkg.rms_norm_quantize_rows(y2[:, :q_cols], mod, nb, 1.1920929e-07, scale_is_mod=True)
+    y1, q1, s1 = pkg.linear_requant(qx, sx, packed, sw, n=n, w_layout=pkg.W_SLAB128, gate=gate.to(dev), residual=resd,
+                                    out_dtype=torch.float32, q_mode=pkg.RQ_RMS, q_cols=q_cols, norm_scale=mod,
+                                    scale_is_mod=True, norm_bias=nb, eps=1.1920929e-07)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    assert torch.equal(y1, y2) and torch.equal(s1, s2) and torch.equal(q1, q2)
