@@ -189,8 +189,10 @@ int b200_w8a8_linear_const_weights(const int8_t *x_i8, const float *x_scales, co
  * layer's :1820-1828), wm_cuda_dequant_silu_quantize_rows_i8 (src/world_cuda_ops.cuh:31-39,
  * src/world_cuda.cu:2129-2137) and wm_cuda_quantize_rows_f32_i8 on a column block of the result.
  * A row's q_cols columns are spread over q_cols / 256 CTAs of one thread-block cluster, which
- * exchange the row statistics through distributed shared memory: q_cols must be a multiple of
- * 256 and at most 2048; N a multiple of 32; all buffers 16-byte aligned with ldq % 16 == 0. */
+ * exchange the row statistics through distributed shared memory: that form needs q_cols a multiple
+ * of 256 and at most 2048, N a multiple of 32, all buffers 16-byte aligned and ldq % 16 == 0.  Anything
+ * else (the MLP hidden of 8192 columns spans 32 tiles, more than a cluster holds) runs as the linear
+ * followed by the stand-alone quantizer on y -- two launches, the same codes -- and then y must be given. */
 #define B200_RQ_PLAIN 1
 #define B200_RQ_RMS 2
 int b200_w8a8_linear_requant(const int8_t *x_i8, const float *x_scales, const int8_t *w_i8, int w_layout,
@@ -199,7 +201,7 @@ int b200_w8a8_linear_requant(const int8_t *x_i8, const float *x_scales, const in
                              int q_mode, int q_cols, const float *norm_scale, int scale_is_mod,
                              const float *norm_bias, float eps, int8_t *q, int64_t ldq, float *q_scales,
                              void *stream);
-/* 0 when b200_w8a8_linear_requant can run this shape / alignment, else 1 (no message). */
+/* 0 when b200_w8a8_linear_requant runs this shape as ONE launch (buffers assumed aligned), else 1 (no message). */
 int b200_w8a8_linear_requant_supported(int m, int k, int n, int q_cols);
 
 /* The fused linear for callers that must not allocate device memory: code running under a

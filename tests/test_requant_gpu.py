@@ -101,14 +101,26 @@ def test_linear_requant_against_oracle(pkg, ref):
     assert torch.equal(q.cpu(), q_ref)
 
 
-def test_linear_requant_rejects_unsupported_width(pkg):
+def test_linear_requant_wide_rows_take_the_two_launch_form(pkg, ref):
+    """The MLP hidden (8192 columns = 32 tiles) is wider than a cluster: linear + GELU -> fp32 y, then the quantizer
+    on y; without y that cannot be done and the call says so."""
     dev = "cuda"
-    qx = torch.zeros(16, 256, dtype=torch.int8, device=dev)
-    sx = torch.ones(16, device=dev)
-    w = torch.zeros(384 * 256, dtype=torch.int8, device=dev)
-    sw = torch.ones(384, device=dev)
-    with pytest.raises(pkg.W8A8Error, match="q_cols"):
-        pkg.linear_requant(qx, sx, w, sw, n=384, w_layout=pkg.W_SLAB128, q_cols=384)
+    m, k, n = 64, 512, 8192
+    x, w, _, _, _, _, _ = _inputs(m, k, n, 5, torch.float32)
+    qx, sx = pkg.quantize_rows(x.to(dev))
+    packed, sw = pkg.pack_weight(w, layout=pkg.W_SLAB128)
+    packed, sw = packed.to(dev), sw.to(dev)
+    y, q, s = pkg.linear_requant(qx, sx, packed, sw, n=n, w_layout=pkg.W_SLAB128, act=pkg.ACT_GELU_TANH,
+                                 out_dtype=torch.float32, q_cols=n)
+    y2 = pkg.linear(qx, sx, packed, sw, n=n, w_layout=pkg.W_SLAB128, act=pkg.ACT_GELU_TANH, out_dtype=torch.float32)
+    q2, s2 = pkg.quantize_rows(y2)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2) and torch.equal(q, q2) and torch.equal(s, s2)
+    qr, sr = ref.quantize_rows(y.cpu())  # the oracle's quantizer on the GPU's own hidden: exact
+    assert torch.equal(q.cpu(), qr) and torch.equal(s.cpu(), sr)
+    with pytest.raises(pkg.W8A8Error, match="needs y"):
+        pkg.linear_requant(qx, sx, packed, sw, n=n, w_layout=pkg.W_SLAB128, act=pkg.ACT_GELU_TANH,
+                           out_dtype=torch.float32, q_cols=n, store_out=False)
 
 
 @pytest.mark.parametrize("m,k,n,q_cols", [(16, 512, 2304, 2048), (200, 256, 1312, 1024), (129, 1024, 512, 512)])

@@ -594,10 +594,22 @@ int linear_requant(const LinearArgs &a_in, const RowQuantSpec &qs, cudaStream_t 
         a.ldo = a.n;
     }
     if (gemm_can_implement(a, true)) return 1;
-    if (const char *why = linear_requant_unsupported(a_in, qs))
-        return fail("linear_requant M=%d K=%d N=%d q_cols=%d cannot run: %s (use the linear followed by the "
-                    "stand-alone quantizer instead)", a.m, a.k, a.n, qs.cols, why);
     if (a.out_dtype == B200_DT_S32) return fail("linear_requant writes fp32, fp16 or bf16");
+    if (const char *why = linear_requant_unsupported(a_in, qs)) {
+        // Rows wider than a cluster holds (the MLP hidden: 32 column tiles) or buffers the fused form cannot
+        // take: with y stored, the same result comes from the linear followed by the stand-alone quantizer
+        // reading y -- two launches, identical codes (the fused kernel quantizes what it stores, too).
+        const bool shape_ok = qs.q && qs.scales && qs.cols > 0 && qs.cols <= a.n && qs.ldq >= qs.cols &&
+                              (qs.mode == B200_RQ_PLAIN || qs.mode == B200_RQ_RMS);
+        if (!a_in.out || !shape_ok)
+            return fail("linear_requant M=%d K=%d N=%d q_cols=%d cannot run fused: %s; the two-launch form needs y "
+                        "and valid q / q_scales", a.m, a.k, a.n, qs.cols, why);
+        if (gemm_launch(a_in, nullptr, 0, stream)) return 1;
+        if (qs.mode == B200_RQ_PLAIN)
+            return quantize_rows(a_in.out, a.out_dtype, a.ldo, qs.q, qs.ldq, qs.scales, a.m, qs.cols, stream);
+        return rms_norm_quantize_rows(a_in.out, a.out_dtype, a.ldo, qs.vec_scale, qs.scale_is_mod, qs.vec_bias, qs.q,
+                                      qs.ldq, qs.scales, a.m, qs.cols, qs.eps, stream);
+    }
     RowqParams rp{};
     GemmParams &p = rp.g;
     p.M = a.m; p.N = a.n; p.K = a.k;
