@@ -290,6 +290,25 @@ size_t b200_w8a8_packed_weight_bytes(int n, int k, int layout);
 int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
                                float *scales_host, int threads);
 
+/* ---- 128 x 128 blockwise numerics (accuracy option) -------------------------------- */
+
+/* The rule the reference's notes name as the next step for accuracy (docs/cuda_w8a8_optimization.md:
+ * 319-321 describes it, :355-356 plans it; the reference tree itself holds no implementation):
+ * activations AND weights carry one scale per 128 x 128 block,
+ *     scale = max(amax, 1e-8) / 128,   code = rne(v / scale) saturated to [-128, 127],
+ * and the linear converts every K block's int32 partial sum to fp32 with that block pair's scales,
+ *     y = 0;  for kb in order:  y = fma(float(acc_kb[r, c]), xs[r / 128][kb] * ws[c / 128][kb], y);  y += bias[c]
+ * in fp32 (the scale product rounded first, one fused multiply-add per K block), then one rounding to
+ * y_dtype.  Scale arrays are [ceil(rows / 128)][K / 128], row-major.
+ * K must be a multiple of 128; code and y buffers 16-byte aligned with 16-byte aligned rows. */
+int b200_w8a8_quantize_blocks128(const void *x, int x_dtype, int64_t ldx, int8_t *q, int64_t ldq, float *block_scales,
+                                 int rows, int cols, void *stream);
+int b200_w8a8_pack_weight_blocks128_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
+                                         float *block_scales_host, int threads);
+int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, const int8_t *w_i8, int w_layout,
+                               const float *w_block_scales, const float *bias, void *y, int y_dtype, int64_t ldy, int m,
+                               int k, int n, void *stream);
+
 /* ---- the linear stack (host-side driver above the operators) ----------------------- */
 
 /* An opaque object that owns the packed int8 weights of n_layers layers plus activation

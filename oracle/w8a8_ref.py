@@ -26,6 +26,10 @@ its probe and its fast-math CUDA build):
   5. GELU(tanh) and SiLU are evaluated in fp32;
   6. fused RMSNorm: sum of squares accumulated in fp64, inv_rms = fp32(1/sqrt(ss/K+eps))
      with correctly rounded fp64 sqrt and division, then separate fp32 multiplies/adds.
+
+The 128 x 128 blockwise functions at the end of the file (`quantize_blocks128`,
+`linear_blocks128`) are PARITY UNPINNED: the reference describes that rule in its notes
+(docs/cuda_w8a8_optimization.md:319-321) but holds neither an implementation nor vectors for it.
 """
 from __future__ import annotations
 
@@ -328,6 +332,67 @@ def stack_forward(x: torch.Tensor, layers: Sequence[LayerWeights], steps: int = 
 def stack_ops_per_row(d: int = D_MODEL, n_qkv: int = N_QKV, hidden: int = D_HIDDEN) -> int:
     """Algorithmic int8 ops per token row per layer: 2 * sum(N*K) over the five linears."""
     return 2 * (n_qkv * d + d * d + d * d + hidden * d + d * hidden)
+
+
+# --------------------------------------------------------------------------------------
+# 128 x 128 blockwise numerics (parity unpinned, see the module docstring)
+# --------------------------------------------------------------------------------------
+def quantize_blocks128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One scale per 128 x 128 block: scale = max(amax, 1e-8) / 128, code = rne(x / scale) saturated to
+    [-128, 127] (the rule docs/cuda_w8a8_optimization.md:319 of the reference quotes).  x [R, C] with C % 128 == 0;
+    a ragged last block row takes its maximum over the rows that exist.  Returns (int8 [R, C], fp32 [ceil(R/128), C/128])."""
+    assert x.ndim == 2 and x.shape[1] % 128 == 0
+    x = x.to(torch.float32)
+    rows, cols = x.shape
+    rb = (rows + 127) // 128
+    xp = torch.zeros(rb * 128, cols, dtype=torch.float32)
+    xp[:rows] = x
+    blocks = xp.view(rb, 128, cols // 128, 128)
+    amax = blocks.abs().amax(dim=(1, 3))
+    scale = torch.clamp(amax, min=1e-8) / 128.0
+    q = torch.round(blocks / scale[:, None, :, None]).clamp(-128, 127).to(torch.int8)
+    return q.view(rb * 128, cols)[:rows].contiguous(), scale
+
+
+def fma_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
+    """Correctly rounded fp32 fused multiply-add a * b + c for fp32 inputs whose product is exact in fp64 (here a is
+    an integer of at most 22 bits).  The product is formed exactly in fp64; adding c rounds once to fp64 and the
+    conversion to fp32 rounds a second time.  Two roundings differ from one only when the fp64 sum sits exactly
+    halfway between two fp32 neighbours while the exact sum does not; the rounding error of the fp64 addition
+    (TwoSum, exact) then says on which side the exact sum lies."""
+    a64, b64, c64 = a.to(torch.float64), b.to(torch.float64), c.to(torch.float64)
+    p = a64 * b64
+    s = p + c64
+    bb = s - p
+    err = (p - (s - bb)) + (c64 - bb)            # s + err == p + c exactly
+    r = s.to(torch.float32)
+    d = s - r.to(torch.float64)                  # exact
+    inf = torch.full_like(r, float("inf"))
+    other = torch.where(d > 0, torch.nextafter(r, inf), torch.nextafter(r, -inf))
+    tie = (d != 0) & ((other.to(torch.float64) - s) == d)
+    toward_other = tie & (err != 0) & ((err > 0) == (d > 0))
+    # on a tie with err pointing back to r's side, r is right only if round-to-even happened to pick that side:
+    # it did pick r, so nothing to do; with err == 0 the tie is real and round-to-even is the IEEE answer
+    return torch.where(toward_other, other, r)
+
+
+def linear_blocks128(qx, sx, qw, sw, bias=None, out_dtype=torch.float16) -> torch.Tensor:
+    """y = 0; for every K block in order y = fma(float(acc_kb), sx[r/128, kb] * sw[c/128, kb], y) in fp32 (the scale
+    product rounded to fp32 first), then + bias, then one rounding to the output type.  acc_kb is the exact int32
+    partial sum of one 128-wide K block (|acc_kb| <= 2^21, so an fp32 matmul of the codes is exact)."""
+    m, k = qx.shape
+    n = qw.shape[0]
+    assert k % 128 == 0 and qw.shape[1] == k
+    rows = torch.arange(m) // 128
+    cols = torch.arange(n) // 128
+    y = torch.zeros(m, n, dtype=torch.float32)
+    for kb in range(k // 128):
+        acc = qx[:, kb * 128:(kb + 1) * 128].to(torch.float32) @ qw[:, kb * 128:(kb + 1) * 128].to(torch.float32).T
+        f = sx[rows, kb][:, None] * sw[cols, kb][None, :]
+        y = fma_f32(acc, f.expand(m, n), y)
+    if bias is not None:
+        y = y + bias.to(torch.float32)[None, :]
+    return y.to(out_dtype)
 
 
 def sqnr_db(reference: torch.Tensor, value: torch.Tensor) -> float:

@@ -1,0 +1,150 @@
+"""The 128 x 128 blockwise numerics (b200_w8a8_quantize_blocks128 / _pack_weight_blocks128_host /
+_linear_blocks128) against the CPU restatement of the rule.  The reference describes this rule in its notes
+(docs/cuda_w8a8_optimization.md:319-321) but ships no implementation of it, so there are no reference vectors."""
+import pytest
+import torch
+
+DEV = "cuda:0"
+
+
+def acts(rows, cols, seed, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g)
+    x[:, : min(cols, 128)] *= 6.0        # one K block with a wider range than the others
+    if rows > 3:
+        x[3] = 0.0
+    return x.to(dtype)
+
+
+def unslab(packed, n, k):
+    return packed.view(k // 128, n, 128).permute(1, 0, 2).reshape(n, k)
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+def test_blockwise_weight_packer_matches_the_oracle(pkg, ref, layout):
+    g = torch.Generator().manual_seed(11)
+    n, k = 200, 384
+    w = torch.randn(n, k, generator=g) * 0.02
+    w[:128, 128:256] = 0.0               # an all-zero block takes the floor scale 1e-8 / 128
+    w[130, 5] = -1.0                     # a block whose extreme is negative reaches code -128
+    packed, scales = pkg.pack_weight_blocks128(w, layout=layout, threads=3)
+    q_ref, s_ref = ref.quantize_blocks128(w)
+    codes = packed.view(n, k) if layout == pkg.W_ROW_MAJOR else unslab(packed, n, k)
+    assert torch.equal(scales.view(torch.int32), s_ref.view(torch.int32))
+    assert torch.equal(codes, q_ref)
+    assert scales[0, 1].item() == torch.tensor(1e-8, dtype=torch.float32).item() / 128 and int(codes[:128, 128:256].abs().max()) == 0
+    assert int(codes.min()) == -128 and int(codes.max()) == 127
+    bad = w.clone()
+    bad[7, 300] = float("inf")
+    with pytest.raises(pkg.W8A8Error, match="not finite"):
+        pkg.pack_weight_blocks128(bad, layout=layout)
+    with pytest.raises(pkg.W8A8Error, match="128"):
+        pkg.pack_weight_blocks128(torch.randn(8, 96), layout=layout)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1, 128), (128, 128), (300, 256), (2048, 2048), (1000, 8192)])
+def test_block_quantizer_bit_exact(pkg, ref, rows, cols, dtype):
+    x = acts(rows, cols, rows + cols, dtype)
+    q, s = pkg.quantize_blocks128(x.to(DEV))
+    q_ref, s_ref = ref.quantize_blocks128(x)
+    assert torch.equal(s.cpu().view(torch.int32), s_ref.view(torch.int32))
+    assert torch.equal(q.cpu(), q_ref)
+
+
+@pytest.mark.gpu
+def test_block_quantizer_rounding_ties_and_extremes(pkg, ref):
+    # every block is scaled so that scale = 2^e exactly: quotients k + 0.5 are then exact ties
+    rows, cols = 256, 256
+    x = torch.zeros(rows, cols)
+    base = torch.arange(-128, 128, dtype=torch.float32)
+    for r in range(rows):
+        x[r] = (base + 0.5).roll(r)[:cols] if cols <= 256 else 0
+    x[0, 0] = 128.0   # amax 128 -> scale 1 in the first block column
+    x[0, 128] = -128.0
+    x[128, 0] = 128.0
+    x[128, 128] = 128.0
+    q, s = pkg.quantize_blocks128(x.to(DEV))
+    q_ref, s_ref = ref.quantize_blocks128(x)
+    assert torch.equal(s.cpu(), s_ref) and float(s_ref[0, 0]) == 1.0
+    assert torch.equal(q.cpu(), q_ref)
+    assert int(q_ref.max()) == 127 and int(q_ref.min()) == -128   # +128 saturates, -128 is kept
+
+
+@pytest.mark.gpu
+def test_block_quantizer_rejects_bad_shapes(pkg):
+    with pytest.raises(pkg.W8A8Error, match="divisible by 128"):
+        pkg.quantize_blocks128(torch.zeros(16, 96, device=DEV))
+    with pytest.raises(pkg.W8A8Error, match="aligned"):
+        pkg.quantize_blocks128(torch.zeros(16, 130, device=DEV, dtype=torch.float16)[:, 1:129])
+
+
+CASES = [  # m, k, n, out dtype, layout, bias
+    (128, 128, 128, torch.float32, 0, False),
+    (100, 256, 200, torch.float16, 1, True),      # ragged rows and columns
+    (16, 2048, 2048, torch.float16, 1, False),    # skinny
+    (512, 2048, 6144, torch.float16, 1, True),    # QKV at 512 rows
+    (2048, 2048, 2048, torch.bfloat16, 1, False),
+    (300, 8192, 2048, torch.float32, 0, True),    # 64 K blocks: every accumulator slot is reused 16 times
+    (1500, 1024, 520, torch.bfloat16, 0, False),  # several tiles per CTA, N not a multiple of 128
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,n,dtype,layout,with_bias", CASES)
+def test_blockwise_linear_bit_exact(pkg, ref, m, k, n, dtype, layout, with_bias):
+    g = torch.Generator().manual_seed(m + k + n)
+    x = acts(m, k, m + n)
+    w = torch.randn(n, k, generator=g) * 0.03
+    w[:, -128:] *= 4.0
+    bias = torch.randn(n, generator=g) * 0.1 if with_bias else None
+    qx, sx = pkg.quantize_blocks128(x.to(DEV))
+    packed, sw = pkg.pack_weight_blocks128(w, layout=layout)
+    y = pkg.linear_blocks128(qx, sx, packed.to(DEV), sw.to(DEV), n=n, w_layout=layout,
+                             bias=None if bias is None else bias.to(DEV), out_dtype=dtype)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    qx_ref, sx_ref = ref.quantize_blocks128(x)
+    qw_ref, sw_ref = ref.quantize_blocks128(w)
+    want = ref.linear_blocks128(qx_ref, sx_ref, qw_ref, sw_ref, bias=bias, out_dtype=dtype)
+    assert torch.equal(y.cpu().view(torch.uint8), want.view(torch.uint8))
+    # and it is a sane linear: close to the fp32 product
+    exact = x.double() @ w.double().T + (0 if bias is None else bias.double())
+    assert ref.sqnr_db(exact.float(), y.cpu().float()) > 30.0
+
+
+@pytest.mark.gpu
+def test_blockwise_beats_rowwise_when_k_ranges_differ(pkg, ref):
+    """What the option is for: a few K segments with a much wider range cost the row/channel rule resolution
+    everywhere else in the row; per-block scales keep it."""
+    g = torch.Generator().manual_seed(5)
+    m, k, n = 256, 2048, 1024
+    x = torch.randn(m, k, generator=g)
+    x[:, 256:384] *= 40.0
+    w = torch.randn(n, k, generator=g) * 0.02
+    w[:, 256:384] *= 0.05       # the wide activations meet small weights: their product is ordinary
+    exact = (x.double() @ w.double().T).float()
+    qx, sx = pkg.quantize_blocks128(x.to(DEV))
+    packed, sw = pkg.pack_weight_blocks128(w)
+    y_blk = pkg.linear_blocks128(qx, sx, packed.to(DEV), sw.to(DEV), n=n, out_dtype=torch.float32)
+    qr, sr = pkg.quantize_rows(x.to(DEV))
+    pw, swr = pkg.pack_weight(w)
+    y_row = pkg.linear(qr, sr, pw.to(DEV), swr.to(DEV), n=n, w_layout=pkg.W_SLAB128, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    blk, row = ref.sqnr_db(exact, y_blk.cpu()), ref.sqnr_db(exact, y_row.cpu())
+    assert blk > row + 6.0, (blk, row)
+
+
+@pytest.mark.gpu
+def test_blockwise_linear_rejects_bad_arguments(pkg):
+    qx = torch.zeros(16, 192, dtype=torch.int8, device=DEV)
+    s = torch.ones(1, 2, device=DEV)
+    w = torch.zeros(128 * 192, dtype=torch.int8, device=DEV)
+    with pytest.raises(pkg.W8A8Error, match="K divisible by 128"):
+        pkg.linear_blocks128(qx, s, w, s, n=128, w_layout=pkg.W_ROW_MAJOR)
+    qx = torch.zeros(16, 256, dtype=torch.int8, device=DEV)
+    w = torch.zeros(100 * 256, dtype=torch.int8, device=DEV)
+    out = torch.empty(16, 104, dtype=torch.float16, device=DEV)[:, 1:101]
+    with pytest.raises(pkg.W8A8Error, match="aligned"):
+        pkg.linear_blocks128(qx, s, w, s, n=100, w_layout=pkg.W_ROW_MAJOR, out=out)

@@ -111,3 +111,33 @@ def test_layer_stack_runs_small(ref):
     y2 = ref.stack_forward(x, [lw, ref.make_layer(1, d, nq, hid)], steps=2)
     assert torch.isfinite(y2.float()).all()
     assert ref.stack_ops_per_row() == 109_051_904
+
+
+def test_fma_f32_is_correctly_rounded(ref):
+    """The oracle's fp32 fused multiply-add against exact rational arithmetic, including the case where rounding
+    to fp64 first and to fp32 second would give the other neighbour."""
+    from fractions import Fraction
+    import numpy as np
+
+    def exact_fma(a, b, c):
+        x = Fraction(float(a)) * Fraction(float(b)) + Fraction(float(c))
+        lo = np.float32(float(x))                       # some nearby fp32; walk to the bracketing pair
+        cands = [lo, np.nextafter(lo, np.float32(np.inf)), np.nextafter(lo, np.float32(-np.inf))]
+        best = min(cands, key=lambda v: (abs(Fraction(float(v)) - x), int(np.float32(v).view(np.uint32)) & 1))
+        return np.float32(best)
+
+    g = torch.Generator().manual_seed(3)
+    a = torch.randint(-(1 << 21), (1 << 21) + 1, (4000,), generator=g).to(torch.float32)
+    b = torch.randn(4000, generator=g) * 1e-4
+    c = torch.randn(4000, generator=g) * torch.tensor([1e-3, 1.0, 1e3, 1e6]).repeat(1000)
+    # crafted: the exact sum lies 2^-60 below the midpoint between two fp32 values; fp64 rounds onto the midpoint,
+    # and round-to-even from there would go UP to the wrong neighbour
+    a = torch.cat([a, torch.tensor([float(2 ** 18 + 1), float(2 ** 18 + 1)])])
+    b = torch.cat([b, torch.tensor([2.0 ** -42 * (1 - 2.0 ** -18), -(2.0 ** -42) * (1 - 2.0 ** -18)])])
+    c = torch.cat([c, torch.tensor([1.0 + 2.0 ** -23, -(1.0 + 2.0 ** -23)])])
+    got = ref.fma_f32(a, b, c)
+    want = torch.tensor([exact_fma(x, y, z) for x, y, z in zip(a.tolist(), b.tolist(), c.tolist())])
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+    assert float(got[-2]) == 1.0 + 2.0 ** -23 and float(got[-1]) == -(1.0 + 2.0 ** -23)
+    naive = (a.double() * b.double() + c.double()).float()
+    assert float(naive[-2]) != float(got[-2])           # the case really needs the correction

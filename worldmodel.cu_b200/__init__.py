@@ -72,6 +72,10 @@ _PROTOTYPES = {
                                                 c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_packed_weight_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200_w8a8_pack_weight_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
+    "b200_w8a8_pack_weight_blocks128_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
+    "b200_w8a8_quantize_blocks128": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
+    "b200_w8a8_linear_blocks128": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+                                           c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_stack_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]),
     "b200_w8a8_stack_destroy": (None, [c_void_p]),
     "b200_w8a8_stack_set_layer": (c_int, [c_void_p, c_int] + [c_void_p] * 8 + [c_int]),
@@ -350,6 +354,43 @@ def pack_weight(w_f32_cpu, layout=W_SLAB128, threads=0):
     _check(lib().b200_w8a8_pack_weight_host(w.data_ptr(), n, k, layout, packed.data_ptr(), scales.data_ptr(), threads),
            "pack_weight_host")
     return packed, scales
+
+
+# ------------------------------------------------------------------ 128 x 128 blockwise numerics
+def pack_weight_blocks128(w_f32_cpu, layout=W_SLAB128, threads=0):
+    """Host fp32 [N,K] -> (int8 packed CPU tensor [N*K], fp32 block scales [ceil(N/128), K/128])."""
+    import torch
+    w = w_f32_cpu.contiguous().to(torch.float32)
+    n, k = w.shape
+    packed = torch.empty(n * k, dtype=torch.int8)
+    scales = torch.empty((n + 127) // 128, max(k // 128, 1), dtype=torch.float32)
+    _check(lib().b200_w8a8_pack_weight_blocks128_host(w.data_ptr(), n, k, layout, packed.data_ptr(), scales.data_ptr(),
+                                                      threads), "pack_weight_blocks128_host")
+    return packed, scales
+
+
+def quantize_blocks128(x):
+    """x: [rows, cols] CUDA tensor (fp32/fp16/bf16), cols % 128 == 0.  Returns (codes int8, block scales
+    [ceil(rows/128), cols/128])."""
+    import torch
+    rows, cols = x.shape
+    q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
+    s = torch.empty((rows + 127) // 128, max(cols // 128, 1), dtype=torch.float32, device=x.device)
+    _check(lib().b200_w8a8_quantize_blocks128(_ptr(x), _dt(x), x.stride(0), _ptr(q), cols, _ptr(s), rows, cols, _stream()),
+           "quantize_blocks128")
+    return q, s
+
+
+def linear_blocks128(x_i8, x_block_scales, w_i8, w_block_scales, n, w_layout=W_SLAB128, bias=None, out_dtype=None,
+                     out=None):
+    import torch
+    m, k = x_i8.shape
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype or torch.float16, device=x_i8.device)
+    _check(lib().b200_w8a8_linear_blocks128(_ptr(x_i8), _ptr(x_block_scales), _ptr(w_i8), w_layout, _ptr(w_block_scales),
+                                            _ptr(bias), _ptr(out), _dt(out), out.stride(0), m, k, n, _stream()),
+           "linear_blocks128")
+    return out
 
 
 def write_weight_file(path, d_model, n_qkv, d_hidden, layers, threads=0):

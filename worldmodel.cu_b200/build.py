@@ -24,6 +24,7 @@ SOURCES = [
     "dequant_ops.cu",
     "gemm_i8_tcgen05.cu",
     "gemm_i8_rowq.cu",
+    "gemm_i8_blocks128.cu",
     "mma_rate.cu",
     "pack_weights.cpp",
     "weight_file.cpp",

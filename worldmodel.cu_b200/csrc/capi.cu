@@ -237,4 +237,35 @@ int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, in
     return pack_weight_host(w_host, n, k, layout, packed_host, scales_host, threads);
 }
 
+int b200_w8a8_pack_weight_blocks128_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
+                                         float *block_scales_host, int threads) {
+    return pack_weight_blocks128_host(w_host, n, k, layout, packed_host, block_scales_host, threads);
+}
+
+int b200_w8a8_quantize_blocks128(const void *x, int x_dtype, int64_t ldx, int8_t *q, int64_t ldq, float *block_scales,
+                                 int rows, int cols, void *stream) {
+    if (status_check_entry()) return 1;
+    return quantize_blocks128(x, x_dtype, ldx, q, ldq, block_scales, rows, cols, as_stream(stream));
+}
+
+int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, const int8_t *w_i8, int w_layout,
+                               const float *w_block_scales, const float *bias, void *y, int y_dtype, int64_t ldy, int m,
+                               int k, int n, void *stream) {
+    if (status_check_entry()) return 1;
+    Blocks128Args a = {};
+    a.x = x_i8;
+    a.x_scales = x_block_scales;
+    a.w = w_i8;
+    a.w_layout = w_layout;
+    a.w_scales = w_block_scales;
+    a.bias = bias;
+    a.out = y;
+    a.ldo = ldy;
+    a.out_dtype = y_dtype;
+    a.m = m;
+    a.k = k;
+    a.n = n;
+    return linear_blocks128(a, as_stream(stream));
+}
+
 }  // extern "C"

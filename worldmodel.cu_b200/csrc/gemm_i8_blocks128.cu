@@ -1,0 +1,467 @@
+// 128 x 128 blockwise W8A8: the accuracy option the reference's notes name as their next step
+// (docs/cuda_w8a8_optimization.md:319-321 for the rule, :355-356 for the plan).  Activations and
+// weights both carry one scale per 128 x 128 block,
+//     scale = max(amax, 1e-8) / 128,   code = rne(x / scale) saturated to [-128, 127],
+// and the GEMM turns the int32 partial sum of every K block into fp32 with that K block's pair of
+// scales before adding it to an fp32 accumulator:
+//     y = 0;  for kb in order:  y = fma(float(acc_kb[m, n]), sa[m / 128, kb] * sw[n / 128, kb], y)
+// (the scale pair's product rounded to fp32 first, then one fused multiply-add per K block, in fp32),
+// then + bias, then one rounding to the output type.
+// The reference tree holds no implementation of this rule (its authors ported a third-party kernel
+// out of tree), so parity here is against this library's own CPU restatement of the rule only.
+//
+// Kernel shape: a 128 x 128 output tile per persistent CTA, so one tile sees exactly one activation
+// block row and one weight block row and a K block's scale pair is a single number.  The tensor core
+// writes K block after K block into four 128-column accumulators of tensor memory in turn; sixteen
+// epilogue warps (four per SM sub-core, so the tensor-memory load of one hides behind the arithmetic
+// of the others) drain each one as soon as it is complete (`tcgen05.ld`, slot handed back at once)
+// and fold it into 32 fp32 registers per thread, while the next three K blocks are already running.
+// int32 -> fp32 is one integer add and one float subtract (|acc| <= 2^21 fits the mantissa of
+// 1.5 * 2^23), which keeps the conversion off the 16-lane conversion unit.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_i8_common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BQ = 128;                              // block edge = tile edge
+constexpr int kBqStageBytes = BM * BK + BQ * BK;     // 16 KB of A + 16 KB of W
+constexpr int kBqStages = 5;
+constexpr int kBqEpilogueWarps = 16;                 // 32 rows x 32 columns of the tile each
+constexpr int kBqThreads = 64 + 32 * kBqEpilogueWarps;
+constexpr int kBqStagingBytes = kBqEpilogueWarps * kStagingPerWarp;
+constexpr int kBqSlots = 4;                          // K-block accumulators in tensor memory
+constexpr int kBqTmemCols = kBqSlots * BQ;           // all 512 columns
+constexpr int kBqBarBytes = (2 * kBqStages + kBqSlots) * 8 + 16;
+constexpr int kBqSmemBytes = kBqStages * kBqStageBytes + kBqStagingBytes + kBqBarBytes + 1024;
+static_assert(kBqSmemBytes <= 227 * 1024, "shared memory of the blockwise GEMM");
+
+// Two fp32 values in one 64-bit register and the two-wide add / fused multiply-add on them: half the
+// instructions of the scalar forms, each half rounded like the scalar instruction.  (A two-wide multiply
+// followed by a two-wide add is not an alternative where separate roundings are wanted: the assembler
+// merges the pair into the fused form even when both carry an explicit rounding mode.)
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, uint32_t &lo, uint32_t &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2_rn(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2_rn(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+struct BlocksParams {
+    GemmParams g;            // shape, raster, output, bias, wait controls
+    const float *a_scales;   // [ceil(M / 128)][K / 128]
+    const float *w_scales;   // [ceil(N / 128)][K / 128]
+};
+
+template <int OUT>
+__global__ void __launch_bounds__(kBqThreads, 1)
+    gemm_i8_blocks128_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                             const __grid_constant__ CUtensorMap tm_out, const BlocksParams bp) {
+    const GemmParams &p = bp.g;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *staging = smem + kBqStages * kBqStageBytes;
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(staging + kBqStagingBytes);
+    // done[s]: the MMAs that read stage s have completed.  One commit per K block serves two waiters: the
+    // producer (the stage may be refilled) and the epilogue warps (the K block's accumulator is complete).
+    uint64_t *bar_done = bar_full + kBqStages;
+    uint64_t *bar_tempty = bar_done + kBqStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + kBqSlots);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kBqStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_done[s], 1);
+        }
+        for (int b = 0; b < kBqSlots; ++b) mbar_init(&bar_tempty[b], kBqEpilogueWarps);
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        tma_prefetch_desc(&tm_out);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kBqTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            pdl_wait();  // the codes of A come from the kernel before this one
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                int m_blk, n_blk;
+                decode_tile(p, tile, m_blk, n_blk);
+                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                    ok = mbar_wait_bounded(&bar_done[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
+                    if (!ok) break;
+                    uint8_t *sa = smem + s * kBqStageBytes;
+                    mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(p.a_stage_bytes + BQ * BK));
+                    tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m_blk * BM, 0);
+                    tma_load_3d(sa + BM * BK, &tm_b, &bar_full[s], kb * p.b_kx, n_blk * BQ, kb * p.b_kz);
+                    if (++s == kBqStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_i8(BM, BQ);
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t g = 0;  // K blocks issued so far by this CTA: slot g % 4, use number g / 4
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                for (int kb = 0; kb < p.num_k_blocks; ++kb, ++g) {
+                    const uint32_t slot = g & (kBqSlots - 1);
+                    const uint32_t use = (g / kBqSlots) & 1u;
+                    ok = mbar_wait_bounded(&bar_tempty[slot], use ^ 1u, wctx, KS_TIMEOUT_TMEM_EMPTY);
+                    if (!ok) break;
+                    ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * kBqStageBytes);
+                    const uint64_t da = umma_smem_desc_k128(sa);
+                    const uint64_t db = umma_smem_desc_k128(sa + (uint32_t)(BM * BK));
+                    const uint32_t d_tmem = tmem_base + slot * (uint32_t)BQ;
+#pragma unroll
+                    for (int j = 0; j < BK / 32; ++j)
+                        umma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (uint32_t)(j != 0));
+                    umma_commit(&bar_done[s]);  // the stage may be refilled, and this K block's sums are complete
+                    if (++s == kBqStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const int ew = warp - 2;
+        const int sub = warp & 3;   // TMEM sub-partition this warp may read
+        const int quarter = ew >> 2;  // which 32 of the tile's 128 columns
+        uint8_t *stage = staging + ew * kStagingPerWarp;
+        pdl_wait();  // the activation block scales come from the kernel before this one
+        uint32_t g = 0;
+        int s = 0;        // the stage whose `done` barrier announces K block g
+        uint32_t ph = 0;
+        int seq = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+            int m_blk, n_blk;
+            decode_tile(p, tile, m_blk, n_blk);
+            const float *sa_row = bp.a_scales + (long long)m_blk * p.num_k_blocks;
+            const float *sw_row = bp.w_scales + (long long)n_blk * p.num_k_blocks;
+            uint64_t acc[16];  // fp32 pairs (columns 2j, 2j+1): the arithmetic below is two-wide
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[j] = 0ull;
+            float f_next = __fmul_rn(__ldg(sa_row), __ldg(sw_row));
+#pragma unroll 1
+            for (int kb = 0; kb < p.num_k_blocks; ++kb, ++g) {
+                const uint32_t slot = g & (kBqSlots - 1);
+                const float f = f_next;
+                if (kb + 1 < p.num_k_blocks) f_next = __fmul_rn(__ldg(sa_row + kb + 1), __ldg(sw_row + kb + 1));
+                ok = mbar_wait_bounded(&bar_done[s], ph, wctx, KS_TIMEOUT_TMEM_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (++s == kBqStages) { s = 0; ph ^= 1u; }
+                tc_fence_after_sync();
+                const uint32_t taddr =
+                    tmem_base + ((uint32_t)(sub * 32) << 16) + slot * (uint32_t)BQ + (uint32_t)(quarter * 32);
+                uint32_t r0[32];
+                tmem_ld_32x32(taddr, r0);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_tempty[slot]);  // the tensor core may overwrite the slot
+                // float(acc) exactly: 1.5 * 2^23 + acc is representable for |acc| <= 2^22 (here <= 2^21)
+                const uint64_t ff = pack2(__float_as_uint(f), __float_as_uint(f));
+                const uint64_t unbias = pack2(__float_as_uint(-12582912.0f), __float_as_uint(-12582912.0f));
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const uint64_t v = add2_rn(pack2(r0[2 * j] + 0x4B400000u, r0[2 * j + 1] + 0x4B400000u), unbias);
+                    acc[j] = fma2_rn(v, ff, acc[j]);
+                }
+            }
+            if (!ok) break;
+            const int row0 = m_blk * BM + sub * 32;
+            const int col0 = n_blk * BQ + quarter * 32;
+            if (col0 < p.N) {  // warp-uniform
+                uint32_t w[32];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) unpack2(acc[j], w[2 * j], w[2 * j + 1]);
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) w[j] = __float_as_uint(__fadd_rn(__uint_as_float(w[j]), __ldg(p.bias + col0 + j)));
+                }
+                stage_and_store<OUT>(p, &tm_out, stage, w, lane, row0, col0, seq++);
+            }
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+    }
+
+    __syncthreads();
+    if (*abort_flag) {
+        // a wait ran out somewhere: give copies and MMAs already in flight time to land before the shared and
+        // tensor memory they target is released
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kBqTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------- the block quantizer
+// One CTA per 128 x 128 block: two threads per row, 64 contiguous elements each, held in registers
+// between the block maximum and the codes, so the input is read once.
+struct BlockScale {
+    float scale, inv;
+};
+__device__ __forceinline__ int block_code(float v, const BlockScale &bs) {
+    // correctly rounded v / scale (one reciprocal per block, Markstein's correction step per element),
+    // rounded to the nearest-even integer by adding 1.5 * 2^23
+    float q;
+    if (bs.inv != 0.0f) {
+        const float q0 = __fmul_rn(v, bs.inv);
+        const float rem = __fmaf_rn(-q0, bs.scale, v);
+        q = __fmaf_rn(rem, bs.inv, q0);
+    } else {
+        q = __fdiv_rn(v, bs.scale);
+    }
+    const int c = __float_as_int(__fadd_rn(q, 12582912.0f)) - 0x4B400000;
+    return max(-128, min(127, c));
+}
+
+template <typename T>
+struct Load64;
+template <>
+struct Load64<float> {
+    static __device__ __forceinline__ void load(const float *src, float (&v)[64]) {
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float4 t = __ldg(s4 + i);
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+    }
+};
+template <>
+struct Load64<__half> {
+    static __device__ __forceinline__ void load(const __half *src, float (&v)[64]) {
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint4 t = __ldg(s4 + i);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+                v[8 * i + 2 * k] = f.x;
+                v[8 * i + 2 * k + 1] = f.y;
+            }
+        }
+    }
+};
+template <>
+struct Load64<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *src, float (&v)[64]) {
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint4 t = __ldg(s4 + i);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {  // a bf16 is the upper half of an fp32
+                v[8 * i + 2 * k] = __uint_as_float(w[k] << 16);
+                v[8 * i + 2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+            }
+        }
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) quant_blocks128_kernel(const T *__restrict__ x, long long ldx,
+                                                               int8_t *__restrict__ q, long long ldq,
+                                                               float *__restrict__ scales, int rows, int k_blocks) {
+    __shared__ float red[8];
+    pdl_trigger();
+    const int kb = blockIdx.x, mb = blockIdx.y;
+    const int r = mb * BQ + (threadIdx.x >> 1);
+    const int c0 = kb * BQ + (threadIdx.x & 1) * 64;
+    const bool live = r < rows;
+    float v[64];
+    pdl_wait();
+    if (live) {
+        Load64<T>::load(x + (long long)r * ldx + c0, v);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) v[j] = 0.0f;
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 64; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    BlockScale bs;
+    bs.scale = __fmul_rn(fmaxf(amax, 1e-8f), 0.0078125f);  // / 128: exact, the result is a normal number
+    bs.inv = bs.scale < 1e30f ? __frcp_rn(bs.scale) : 0.0f;
+    if (threadIdx.x == 0) scales[(long long)mb * k_blocks + kb] = bs.scale;
+    if (!live) return;
+    uint4 *dst = reinterpret_cast<uint4 *>(q + (long long)r * ldq + c0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int b = 16 * i + 4 * k;
+            w[k] = (uint32_t)(block_code(v[b], bs) & 0xFF) | ((uint32_t)(block_code(v[b + 1], bs) & 0xFF) << 8) |
+                   ((uint32_t)(block_code(v[b + 2], bs) & 0xFF) << 16) |
+                   ((uint32_t)(block_code(v[b + 3], bs) & 0xFF) << 24);
+        }
+        dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+struct BlocksDeviceInfo {
+    bool attr_set[3] = {};
+};
+BlocksDeviceInfo &blocks_device_info(int dev) {
+    static BlocksDeviceInfo info[64];
+    return info[dev & 63];
+}
+
+template <int OUT>
+int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
+    BlocksDeviceInfo &di = blocks_device_info(dev);
+    constexpr int oi = OUT == B200_DT_F32 ? 0 : (OUT == B200_DT_F16 ? 1 : 2);
+    if (ensure_smem_attr(di.attr_set[oi], gemm_i8_blocks128_kernel<OUT>, kBqSmemBytes, "gemm_i8_blocks128_kernel"))
+        return 1;
+    BlocksParams bp;
+    memset(&bp, 0, sizeof(bp));
+    GemmParams &p = bp.g;
+    p.M = a.m;
+    p.N = a.n;
+    p.K = a.k;
+    p.num_m_blocks = (a.m + BM - 1) / BM;
+    p.num_n_blocks = (a.n + BQ - 1) / BQ;
+    p.num_tiles = p.num_m_blocks * p.num_n_blocks;
+    p.num_k_blocks = a.k / BK;
+    p.group_m = 32;
+    p.splits = 1;
+    p.num_work = p.num_tiles;
+    const int a_rows = a.m >= BM ? BM : ((a.m + 15) / 16) * 16;
+    p.a_stage_bytes = a_rows * BK;
+    p.bias = a.bias;
+    p.out = a.out;
+    p.ldo = a.ldo;
+    p.out_dtype = a.out_dtype;
+    p.tma_store = 1;
+    p.status = status_slot(true);
+    p.wait_limit_ns = wait_limit_ns();
+    bp.a_scales = a.x_scales;
+    bp.w_scales = a.w_scales;
+    CUtensorMap tm_a, tm_b, tm_out;
+    if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m,
+                 (uint32_t)a_rows))
+        return 1;
+    if (a.w_layout == B200_W_SLAB128) {
+        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, BQ)) return 1;
+        p.b_kx = 0;
+        p.b_kz = 1;
+    } else {
+        if (make_map(&tm_b, a.w, (uint64_t)a.k, (uint64_t)a.n, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.n, BQ))
+            return 1;
+        p.b_kx = BK;
+        p.b_kz = 0;
+    }
+    if (make_out_map(&tm_out, a.out, a.out_dtype, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldo)) return 1;
+    const int sms = device_sms();
+    const int grid = p.num_tiles < sms ? p.num_tiles : sms;
+    cudaError_t le = launch_kernel(gemm_i8_blocks128_kernel<OUT>, dim3((unsigned)grid), dim3(kBqThreads),
+                                   (size_t)kBqSmemBytes, stream, tm_a, tm_b, tm_out, bp);
+    if (le != cudaSuccess) return fail("launching gemm_i8_blocks128: %s", cudaGetErrorString(le));
+    return check_launch("gemm_i8_blocks128");
+}
+
+}  // namespace
+
+int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
+                       int cols, cudaStream_t stream) {
+    if (!x || !q || !scales || rows <= 0 || cols <= 0) return fail("invalid quantize_blocks128 arguments");
+    if (cols % BQ != 0) return fail("quantize_blocks128 needs a column count divisible by 128, got %d", cols);
+    const size_t esz = in_dtype == B200_DT_F32 ? 4 : 2;
+    if (in_dtype != B200_DT_F32 && in_dtype != B200_DT_F16 && in_dtype != B200_DT_BF16)
+        return fail("quantize_blocks128 reads fp32, fp16 or bf16");
+    if (ldx < cols || ldq < cols || !aligned16(x) || !aligned16(q) || ((size_t)ldx * esz) % 16 != 0 || ldq % 16 != 0)
+        return fail("quantize_blocks128 needs 16-byte aligned buffers and row strides (ldx=%lld, ldq=%lld)", ldx, ldq);
+    const dim3 grid((unsigned)(cols / BQ), (unsigned)((rows + BQ - 1) / BQ));
+    if (grid.y > 65535u) return fail("quantize_blocks128: more than 65535 block rows");
+    cudaError_t e;
+    if (in_dtype == B200_DT_F32)
+        e = launch_kernel(quant_blocks128_kernel<float>, grid, dim3(256), 0, stream, (const float *)x, ldx, q, ldq, scales,
+                          rows, cols / BQ);
+    else if (in_dtype == B200_DT_F16)
+        e = launch_kernel(quant_blocks128_kernel<__half>, grid, dim3(256), 0, stream, (const __half *)x, ldx, q, ldq,
+                          scales, rows, cols / BQ);
+    else
+        e = launch_kernel(quant_blocks128_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16 *)x,
+                          ldx, q, ldq, scales, rows, cols / BQ);
+    if (e != cudaSuccess) return fail("launching quant_blocks128: %s", cudaGetErrorString(e));
+    return check_launch("quant_blocks128");
+}
+
+int linear_blocks128(const Blocks128Args &a, cudaStream_t stream) {
+    if (!a.x || !a.w || !a.x_scales || !a.w_scales || !a.out) return fail("linear_blocks128: null operand");
+    if (a.m <= 0 || a.n <= 0 || a.k <= 0) return fail("linear_blocks128: bad shape M=%d K=%d N=%d", a.m, a.k, a.n);
+    if (a.k % BK != 0) return fail("linear_blocks128 needs K divisible by 128, got K=%d", a.k);
+    if (a.w_layout != B200_W_ROW_MAJOR && a.w_layout != B200_W_SLAB128) return fail("unknown weight layout %d", a.w_layout);
+    if (a.out_dtype != B200_DT_F32 && a.out_dtype != B200_DT_F16 && a.out_dtype != B200_DT_BF16)
+        return fail("linear_blocks128 writes fp32, fp16 or bf16");
+    const size_t esz = a.out_dtype == B200_DT_F32 ? 4 : 2;
+    if (!aligned16(a.x) || !aligned16(a.w)) return fail("linear_blocks128: codes must be 16-byte aligned");
+    if (a.ldo < a.n || !aligned16(a.out) || ((size_t)a.ldo * esz) % 16 != 0)
+        return fail("linear_blocks128: y must be 16-byte aligned with 16-byte aligned rows (ldo=%lld)", a.ldo);
+    switch (a.out_dtype) {
+        case B200_DT_F32: return launch_blocks128<B200_DT_F32>(a, stream);
+        case B200_DT_F16: return launch_blocks128<B200_DT_F16>(a, stream);
+        default: return launch_blocks128<B200_DT_BF16>(a, stream);
+    }
+}
+
+}  // namespace b200

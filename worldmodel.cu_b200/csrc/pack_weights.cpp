@@ -74,4 +74,55 @@ int pack_weight_host(const float *w, int n, int k, int layout, int8_t *packed, f
     return 0;
 }
 
+// The 128 x 128 blockwise rule (docs/cuda_w8a8_optimization.md:319-321 of the reference describes it):
+// one scale per block, scale = max(amax, 1e-8) / 128, codes rne(w / scale) saturated to [-128, 127];
+// scales[ceil(n / 128)][k / 128].  Block rows are independent and go to separate host threads.
+int pack_weight_blocks128_host(const float *w, int n, int k, int layout, int8_t *packed, float *scales, int threads) {
+    if (!w || !packed || !scales || n <= 0 || k <= 0) return fail("invalid pack_weight_blocks128 arguments N=%d K=%d", n, k);
+    if (layout != B200_W_ROW_MAJOR && layout != B200_W_SLAB128) return fail("unknown weight layout %d", layout);
+    if ((k % 128) != 0) return fail("blockwise weights need K %% 128 == 0, got K=%d", k);
+    const int nb = (n + 127) / 128, kbs = k / 128;
+    if (threads <= 0) threads = (int)std::thread::hardware_concurrency();
+    if (threads <= 0) threads = 1;
+    if (threads > nb) threads = nb;
+    std::atomic<int> bad_row(-1), bad_col(-1);
+    std::atomic<int> next(0);
+    auto work = [&]() {
+        for (int b = next.fetch_add(1); b < nb; b = next.fetch_add(1)) {
+            const int r0 = b * 128, r1 = r0 + 128 > n ? n : r0 + 128;
+            for (int kb = 0; kb < kbs; ++kb) {
+                float amax = 0.0f;
+                for (int row = r0; row < r1; ++row) {
+                    const float *src = w + (size_t)row * k + (size_t)kb * 128;
+                    for (int c = 0; c < 128; ++c) {
+                        if (!isfinite(src[c])) {
+                            int expect = -1;
+                            if (bad_row.compare_exchange_strong(expect, row)) bad_col.store(kb * 128 + c);
+                            return;
+                        }
+                        amax = fmaxf(amax, fabsf(src[c]));
+                    }
+                }
+                const float scale = fmaxf(amax, 1e-8f) / 128.0f;
+                scales[(size_t)b * kbs + kb] = scale;
+                for (int row = r0; row < r1; ++row) {
+                    const float *src = w + (size_t)row * k + (size_t)kb * 128;
+                    int8_t *dst = layout == B200_W_ROW_MAJOR ? packed + (size_t)row * k + (size_t)kb * 128
+                                                             : packed + ((size_t)kb * n + row) * 128;
+                    for (int c = 0; c < 128; ++c) {
+                        int v = (int)nearbyintf(src[c] / scale);  // ties to even in the default rounding mode
+                        dst[c] = (int8_t)(v < -128 ? -128 : (v > 127 ? 127 : v));
+                    }
+                }
+            }
+        }
+    };
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t) pool.emplace_back(work);
+    for (auto &th : pool) th.join();
+    if (bad_row.load() >= 0)
+        return fail("weight matrix [%d,%d] holds a value that is not finite at row %d, column %d", n, k, bad_row.load(), bad_col.load());
+    return 0;
+}
+
 }  // namespace b200

@@ -154,6 +154,24 @@ int gemm_launch(const LinearArgs &a, void *workspace, size_t workspace_bytes, cu
 size_t gemm_workspace_size(int m, int k, int n);
 void gemm_reset_static_tickets();
 
+// ---- gemm_i8_blocks128.cu: the 128 x 128 blockwise numerics (one scale per block of activations and of weights,
+// scale = max(amax, 1e-8) / 128, codes in [-128, 127], fp32 accumulation K block by K block)
+struct Blocks128Args {
+    const int8_t *x;         // codes [m, k], row stride k
+    const float *x_scales;   // [ceil(m / 128)][k / 128]
+    const int8_t *w;         // codes, row-major [n, k] or slab layout
+    int w_layout;
+    const float *w_scales;   // [ceil(n / 128)][k / 128]
+    const float *bias;       // [n], nullable
+    void *out;               // [m, ldo]
+    long long ldo;
+    int out_dtype;           // fp32, fp16 or bf16
+    int m, k, n;
+};
+int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
+                       int cols, cudaStream_t stream);
+int linear_blocks128(const Blocks128Args &a, cudaStream_t stream);
+
 // ---- status.cu
 // Device-visible address of the status word (pinned host memory mapped into the device when
 // may_allocate allows creating it, else a __device__ variable).
@@ -181,6 +199,7 @@ int mma_issue_rate(int slabs_per_cta, double *tera_ops_per_s);
 // ---- pack_weights.cpp
 int pack_weight_host(const float *w, int n, int k, int layout, int8_t *packed, float *scales, int threads);
 size_t packed_weight_bytes(int n, int k, int layout);
+int pack_weight_blocks128_host(const float *w, int n, int k, int layout, int8_t *packed, float *scales, int threads);
 
 // ---- weight_file.cpp (host only)
 struct WeightFileWriter;
