@@ -687,6 +687,10 @@ def run_extras(pkg, ref, stack, stream, peaks):
     out["cfg4_skinny"] = run_skinny(pkg, stream, peaks)
     out["qkv_heads_t512"] = run_qkv_heads(pkg, stream)
     try:
+        out["blockwise_128x128_m8192"] = run_blockwise(pkg, stream)
+    except Exception as exc:
+        out["blockwise_128x128_m8192"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    try:
         out["reference_layer_t512"] = run_reference_layer(pkg, stream)
     except Exception as exc:
         out["reference_layer_t512"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
@@ -763,6 +767,60 @@ def run_reference_layer(pkg, stream, tokens=512, n_heads=32, d_head=64):
     else:
         out["reference_cuda_ops"] = {"unavailable": why_not}
     drv.close()
+    return out
+
+
+def run_blockwise(pkg, stream, rows=8192, n_weights=8):
+    """The 128 x 128 blockwise numerics (block quantizer + linear with per-K-block fp32 accumulation) next to the
+    row/channel rule (row quantizer + fused linear) on the layer's shapes at one band of rows, fp16 in and out,
+    graph replay over several distinct weight matrices per shape."""
+    import torch
+    dev = "cuda"
+    out = {"rows": rows}
+    for name, k, n in (("qkv", D_MODEL, N_QKV), ("out", D_MODEL, D_MODEL), ("down", D_HIDDEN, D_MODEL)):
+        x = torch.randn(rows, k, device=dev, dtype=torch.float16)
+        y = torch.empty(rows, n, device=dev, dtype=torch.float16)
+        wq = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(n_weights)]
+        sw_blk = torch.rand((n + 127) // 128, k // 128, device=dev) * 1e-4 + 1e-5
+        sw_row = torch.rand(n, device=dev) * 1e-4 + 1e-5
+        qb, sb = pkg.quantize_blocks128(x)
+        qr, sr = pkg.quantize_rows(x)
+
+        def lin_blocks():
+            for w in wq:
+                pkg.linear_blocks128(qb, sb, w, sw_blk, n=n, out=y)
+
+        def lin_rows():
+            for w in wq:
+                pkg.linear(qr, sr, w, sw_row, n=n, w_layout=pkg.W_SLAB128, out=y, const_weights=True)
+
+        def quant_blocks():
+            for _ in wq:
+                pkg.lib().b200_w8a8_quantize_blocks128(x.data_ptr(), pkg.DT_F16, k, qb.data_ptr(), k, sb.data_ptr(), rows, k,
+                                                       torch.cuda.current_stream().cuda_stream)
+
+        def quant_rows():
+            for _ in wq:
+                pkg.lib().b200_w8a8_quantize_rows(x.data_ptr(), pkg.DT_F16, k, qr.data_ptr(), k, sr.data_ptr(), rows, k,
+                                                  torch.cuda.current_stream().cuda_stream)
+
+        res = {}
+        for key, run in (("blockwise_linear_us", lin_blocks), ("row_channel_linear_us", lin_rows),
+                         ("block_quantizer_us", quant_blocks), ("row_quantizer_us", quant_rows)):
+            with torch.cuda.stream(stream):
+                run()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                run()
+            with torch.cuda.stream(stream):
+                graph.replay()
+            ms, _, _ = time_steps(graph.replay, 5, stream, lambda: None)
+            res[key] = ms / (5 * n_weights) * 1e3
+        ops = 2.0 * rows * k * n
+        res["blockwise_tops"] = ops / res["blockwise_linear_us"] * 1e-6
+        res["row_channel_tops"] = ops / res["row_channel_linear_us"] * 1e-6
+        out[f"{name}_{k}x{n}"] = res
     return out
 
 

@@ -241,8 +241,6 @@ __global__ void __launch_bounds__(kBqThreads, 1)
 }
 
 // ---------------------------------------------------------------- the block quantizer
-// One CTA per 128 x 128 block: two threads per row, 64 contiguous elements each, held in registers
-// between the block maximum and the codes, so the input is read once.
 struct BlockScale {
     float scale, inv;
 };
@@ -262,24 +260,24 @@ __device__ __forceinline__ int block_code(float v, const BlockScale &bs) {
 }
 
 template <typename T>
-struct Load64;
+struct Load32;
 template <>
-struct Load64<float> {
-    static __device__ __forceinline__ void load(const float *src, float (&v)[64]) {
+struct Load32<float> {
+    static __device__ __forceinline__ void load(const float *src, float (&v)[32]) {
         const float4 *s4 = reinterpret_cast<const float4 *>(src);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 8; ++i) {
             const float4 t = __ldg(s4 + i);
             v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
         }
     }
 };
 template <>
-struct Load64<__half> {
-    static __device__ __forceinline__ void load(const __half *src, float (&v)[64]) {
+struct Load32<__half> {
+    static __device__ __forceinline__ void load(const __half *src, float (&v)[32]) {
         const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
             const uint4 t = __ldg(s4 + i);
             const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -292,11 +290,11 @@ struct Load64<__half> {
     }
 };
 template <>
-struct Load64<__nv_bfloat16> {
-    static __device__ __forceinline__ void load(const __nv_bfloat16 *src, float (&v)[64]) {
+struct Load32<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *src, float (&v)[32]) {
         const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
             const uint4 t = __ldg(s4 + i);
             const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -308,34 +306,36 @@ struct Load64<__nv_bfloat16> {
     }
 };
 
+// One CTA of 512 threads per 128 x 128 block: four threads per row, 32 contiguous elements each, held in
+// registers between the block maximum and the codes, so the input is read once; two CTAs fit an SM.
 template <typename T>
-__global__ void __launch_bounds__(256) quant_blocks128_kernel(const T *__restrict__ x, long long ldx,
-                                                               int8_t *__restrict__ q, long long ldq,
-                                                               float *__restrict__ scales, int rows, int k_blocks) {
-    __shared__ float red[8];
+__global__ void __launch_bounds__(512, 2) quant_blocks128_kernel(const T *__restrict__ x, long long ldx,
+                                                                  int8_t *__restrict__ q, long long ldq,
+                                                                  float *__restrict__ scales, int rows, int k_blocks) {
+    __shared__ float red[16];
     pdl_trigger();
     const int kb = blockIdx.x, mb = blockIdx.y;
-    const int r = mb * BQ + (threadIdx.x >> 1);
-    const int c0 = kb * BQ + (threadIdx.x & 1) * 64;
+    const int r = mb * BQ + (threadIdx.x >> 2);
+    const int c0 = kb * BQ + (threadIdx.x & 3) * 32;
     const bool live = r < rows;
-    float v[64];
+    float v[32];
     pdl_wait();
     if (live) {
-        Load64<T>::load(x + (long long)r * ldx + c0, v);
+        Load32<T>::load(x + (long long)r * ldx + c0, v);
     } else {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) v[j] = 0.0f;
+        for (int j = 0; j < 32; ++j) v[j] = 0.0f;
     }
     float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 64; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
     __syncthreads();
     amax = red[0];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    for (int i = 1; i < 16; ++i) amax = fmaxf(amax, red[i]);
     BlockScale bs;
     bs.scale = __fmul_rn(fmaxf(amax, 1e-8f), 0.0078125f);  // / 128: exact, the result is a normal number
     bs.inv = bs.scale < 1e30f ? __frcp_rn(bs.scale) : 0.0f;
@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(256) quant_blocks128_kernel(const T *__restric
     if (!live) return;
     uint4 *dst = reinterpret_cast<uint4 *>(q + (long long)r * ldq + c0);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -434,13 +434,13 @@ int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, lo
     if (grid.y > 65535u) return fail("quantize_blocks128: more than 65535 block rows");
     cudaError_t e;
     if (in_dtype == B200_DT_F32)
-        e = launch_kernel(quant_blocks128_kernel<float>, grid, dim3(256), 0, stream, (const float *)x, ldx, q, ldq, scales,
+        e = launch_kernel(quant_blocks128_kernel<float>, grid, dim3(512), 0, stream, (const float *)x, ldx, q, ldq, scales,
                           rows, cols / BQ);
     else if (in_dtype == B200_DT_F16)
-        e = launch_kernel(quant_blocks128_kernel<__half>, grid, dim3(256), 0, stream, (const __half *)x, ldx, q, ldq,
+        e = launch_kernel(quant_blocks128_kernel<__half>, grid, dim3(512), 0, stream, (const __half *)x, ldx, q, ldq,
                           scales, rows, cols / BQ);
     else
-        e = launch_kernel(quant_blocks128_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16 *)x,
+        e = launch_kernel(quant_blocks128_kernel<__nv_bfloat16>, grid, dim3(512), 0, stream, (const __nv_bfloat16 *)x,
                           ldx, q, ldq, scales, rows, cols / BQ);
     if (e != cudaSuccess) return fail("launching quant_blocks128: %s", cudaGetErrorString(e));
     return check_launch("quant_blocks128");
