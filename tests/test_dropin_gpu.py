@@ -104,3 +104,44 @@ def test_dropin_sequence_matches_oracle(tmp_path, pkg, ref, parity_log):
     acc = ref.gemm_i8_i32(q6, i8("wfc2", D, HID))
     assert same(i32("acc_fc2", T, D), acc)
     assert same(f("next", T, D), ref.dequant_gated_residual(acc, s6, f("sfc2", D), after_ctrl, f("g1", D)))
+
+
+@pytest.mark.gpu
+def test_operators_from_two_host_threads_on_their_own_streams(pkg, ref):
+    """The operators keep no per-call state outside their arguments: two host threads, each with its own stream,
+    buffers and shapes, run quantizer + fused linear 40 times at once and both get the oracle's bits."""
+    import threading
+
+    results, errors = {}, []
+
+    def worker(idx, m, k, n):
+        try:
+            g = torch.Generator().manual_seed(100 + idx)
+            x = (torch.randn(m, k, generator=g) * 0.7).to(torch.float16)
+            w = torch.randn(n, k, generator=g) * 0.02
+            bias = torch.randn(n, generator=g) * 0.1
+            packed, sw = pkg.pack_weight(w, layout=pkg.W_SLAB128)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                xd, pd, swd, bd = x.to("cuda"), packed.to("cuda"), sw.to("cuda"), bias.to("cuda")
+                outs = []
+                for _ in range(40):
+                    q, s = pkg.quantize_rows(xd)
+                    outs.append(pkg.linear(q, s, pd, swd, n=n, w_layout=pkg.W_SLAB128, bias=bd, out_dtype=torch.float16))
+            stream.synchronize()
+            qr, sr = ref.quantize_rows(x)
+            qw, swr = ref.quantize_weight(w)
+            want = ref.linear_w8a8(qr, sr, qw, swr, bias=bias, out_dtype=torch.float16)
+            results[idx] = all(torch.equal(o.cpu().view(torch.uint8), want.view(torch.uint8)) for o in outs)
+        except Exception as exc:  # surfaced in the main thread below
+            errors.append(repr(exc))
+
+    threads = [threading.Thread(target=worker, args=(0, 512, 2048, 2048)),
+               threading.Thread(target=worker, args=(1, 48, 1024, 6144))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert results == {0: True, 1: True}
+    assert pkg.poll_status() == 0
