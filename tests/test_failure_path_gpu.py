@@ -91,3 +91,30 @@ def test_row_quantizing_linear_times_out_cleanly(pkg, short_waits):
     torch.cuda.synchronize()
     assert all(torch.equal(a, b) for a, b in zip(good, again))
     assert pkg.poll_status() == 0
+
+
+def test_blockwise_linear_times_out_cleanly(pkg, ref, short_waits):
+    """The 128 x 128 blockwise kernel: its MMA issuer gives up, the sixteen epilogue warps and the producer see the
+    abort flag and drain, tensor memory is returned, and the next call is exact."""
+    L = short_waits
+    g = torch.Generator().manual_seed(6)
+    m, k, n = 300, 512, 264
+    x = torch.randn(m, k, generator=g)
+    w = torch.randn(n, k, generator=g) * 0.03
+    qx, sx = pkg.quantize_blocks128(x.to(DEV))
+    packed, sw = pkg.pack_weight_blocks128(w)
+    packed, sw = packed.to(DEV), sw.to(DEV)
+    qx_ref, sx_ref = ref.quantize_blocks128(x)
+    qw_ref, sw_ref = ref.quantize_blocks128(w)
+    want = ref.linear_blocks128(qx_ref, sx_ref, qw_ref, sw_ref, out_dtype=torch.float16)
+    L.b200_w8a8_debug_drop_operand_load(1)
+    pkg.linear_blocks128(qx, sx, packed, sw, n=n)      # launches; every CTA loses its first A tile
+    torch.cuda.synchronize()
+    # the MMA issuer (waiting for operands, 102) and the epilogue warps (waiting for the accumulator, 104) run
+    # out at about the same moment; whichever is first leaves its code
+    with pytest.raises(pkg.W8A8Error, match="gave up a bounded wait.*status 10[24]"):
+        pkg.linear_blocks128(qx, sx, packed, sw, n=n)
+    y = pkg.linear_blocks128(qx, sx, packed, sw, n=n)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    assert torch.equal(y.cpu().view(torch.uint8), want.view(torch.uint8))

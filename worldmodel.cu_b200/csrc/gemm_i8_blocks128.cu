@@ -123,7 +123,9 @@ __global__ void __launch_bounds__(kBqThreads, 1)
                     if (!ok) break;
                     uint8_t *sa = smem + s * kBqStageBytes;
                     mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(p.a_stage_bytes + BQ * BK));
-                    tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m_blk * BM, 0);
+                    // test aid: leaving out the very first A tile makes the MMA issuer's wait run out
+                    const bool drop = p.debug_drop_a_load && tile == (int)blockIdx.x && kb == 0;
+                    if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m_blk * BM, 0);
                     tma_load_3d(sa + BM * BK, &tm_b, &bar_full[s], kb * p.b_kx, n_blk * BQ, kb * p.b_kz);
                     if (++s == kBqStages) { s = 0; ph ^= 1u; }
                 }
@@ -394,6 +396,7 @@ int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
     p.tma_store = 1;
     p.status = status_slot(true);
     p.wait_limit_ns = wait_limit_ns();
+    p.debug_drop_a_load = take_debug_drop();
     bp.a_scales = a.x_scales;
     bp.w_scales = a.w_scales;
     CUtensorMap tm_a, tm_b, tm_out;
