@@ -376,9 +376,11 @@ def fma_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
     return torch.where(toward_other, other, r)
 
 
-def linear_blocks128(qx, sx, qw, sw, bias=None, out_dtype=torch.float16) -> torch.Tensor:
+def linear_blocks128(qx, sx, qw, sw, bias=None, out_dtype=torch.float16, act=ACT_NONE, gate=None,
+                     residual=None) -> torch.Tensor:
     """y = 0; for every K block in order y = fma(float(acc_kb), sx[r/128, kb] * sw[c/128, kb], y) in fp32 (the scale
-    product rounded to fp32 first), then + bias, then one rounding to the output type.  acc_kb is the exact int32
+    product rounded to fp32 first), then the epilogue of `epilogue_f32` (+ bias, activation, * gate, + residual) and one
+    rounding to the output type.  acc_kb is the exact int32
     partial sum of one 128-wide K block (|acc_kb| <= 2^21, so an fp32 matmul of the codes is exact)."""
     m, k = qx.shape
     n = qw.shape[0]
@@ -392,6 +394,11 @@ def linear_blocks128(qx, sx, qw, sw, bias=None, out_dtype=torch.float16) -> torc
         y = fma_f32(acc, f.expand(m, n), y)
     if bias is not None:
         y = y + bias.to(torch.float32)[None, :]
+    y = activation(y, act)
+    if gate is not None:
+        y = y * gate.to(torch.float32)[None, :]
+    if residual is not None:
+        y = residual.to(torch.float32) + y
     return y.to(out_dtype)
 
 

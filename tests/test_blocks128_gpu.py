@@ -115,6 +115,62 @@ def test_blockwise_linear_bit_exact(pkg, ref, m, k, n, dtype, layout, with_bias)
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("parts", ["res", "gate_res", "all"])
+def test_blockwise_linear_gate_and_residual_bit_exact(pkg, ref, dtype, parts):
+    """The row/channel linear's epilogue on top of the blockwise accumulation: no transcendental, so exact."""
+    m, k, n = 300, 512, 264
+    g = torch.Generator().manual_seed(17)
+    x = acts(m, k, 3)
+    w = torch.randn(n, k, generator=g) * 0.03
+    bias = torch.randn(n, generator=g) * 0.1 if parts == "all" else None
+    gate = torch.randn(n, generator=g) if parts in ("gate_res", "all") else None
+    res = torch.randn(m, n, generator=g).to(dtype)
+    qx, sx = pkg.quantize_blocks128(x.to(DEV))
+    packed, sw = pkg.pack_weight_blocks128(w)
+    dv = lambda t: None if t is None else t.to(DEV)
+    y = pkg.linear_blocks128(qx, sx, packed.to(DEV), sw.to(DEV), n=n, bias=dv(bias), gate=dv(gate), residual=dv(res),
+                             out_dtype=dtype)
+    torch.cuda.synchronize()
+    qx_ref, sx_ref = ref.quantize_blocks128(x)
+    qw_ref, sw_ref = ref.quantize_blocks128(w)
+    want = ref.linear_blocks128(qx_ref, sx_ref, qw_ref, sw_ref, bias=bias, gate=gate, residual=res, out_dtype=dtype)
+    assert torch.equal(y.cpu().view(torch.uint8), want.view(torch.uint8))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("act", [1, 2])
+def test_blockwise_linear_activation_then_block_requantization(pkg, ref, act):
+    """MLP shape of the layer: fc1 + SiLU / GELU in fp32, block quantizer on the hidden, fc2 + residual.  The
+    activation uses the hardware exp2 / reciprocal like the row/channel epilogue: a few fp32 ulp."""
+    m, k, n = 256, 512, 1024
+    g = torch.Generator().manual_seed(23)
+    x = acts(m, k, 4)
+    w1 = torch.randn(n, k, generator=g) * 0.03
+    b1 = torch.randn(n, generator=g) * 0.1
+    w2 = torch.randn(k, n, generator=g) * 0.03
+    res = torch.randn(m, k, generator=g)
+    qx, sx = pkg.quantize_blocks128(x.to(DEV))
+    p1, s1 = pkg.pack_weight_blocks128(w1)
+    p2, s2 = pkg.pack_weight_blocks128(w2)
+    h = pkg.linear_blocks128(qx, sx, p1.to(DEV), s1.to(DEV), n=n, bias=b1.to(DEV), act=act, out_dtype=torch.float32)
+    qh, sh = pkg.quantize_blocks128(h)
+    y = pkg.linear_blocks128(qh, sh, p2.to(DEV), s2.to(DEV), n=k, residual=res.to(DEV), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    qx_ref, sx_ref = ref.quantize_blocks128(x)
+    q1, t1 = ref.quantize_blocks128(w1)
+    q2, t2 = ref.quantize_blocks128(w2)
+    h_ref = ref.linear_blocks128(qx_ref, sx_ref, q1, t1, bias=b1, act=act, out_dtype=torch.float32)
+    assert torch.allclose(h.cpu(), h_ref, rtol=4e-6, atol=1e-6)
+    # downstream of the GPU's own hidden everything is exact again
+    qh_ref, sh_ref = ref.quantize_blocks128(h.cpu())
+    assert torch.equal(qh.cpu(), qh_ref) and torch.equal(sh.cpu(), sh_ref)
+    want = ref.linear_blocks128(qh_ref, sh_ref, q2, t2, residual=res, out_dtype=torch.float32)
+    assert torch.equal(y.cpu().view(torch.uint8), want.view(torch.uint8))
+
+
+@pytest.mark.gpu
 def test_blockwise_beats_rowwise_when_k_ranges_differ(pkg, ref):
     """What the option is for: a few K segments with a much wider range cost the row/channel rule resolution
     everywhere else in the row; per-block scales keep it."""

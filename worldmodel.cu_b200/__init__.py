@@ -74,8 +74,8 @@ _PROTOTYPES = {
     "b200_w8a8_pack_weight_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "b200_w8a8_pack_weight_blocks128_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "b200_w8a8_quantize_blocks128": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
-    "b200_w8a8_linear_blocks128": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int64,
-                                           c_int, c_int, c_int, c_void_p]),
+    "b200_w8a8_linear_blocks128": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_stack_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]),
     "b200_w8a8_stack_destroy": (None, [c_void_p]),
     "b200_w8a8_stack_set_layer": (c_int, [c_void_p, c_int] + [c_void_p] * 8 + [c_int]),
@@ -381,15 +381,16 @@ def quantize_blocks128(x):
     return q, s
 
 
-def linear_blocks128(x_i8, x_block_scales, w_i8, w_block_scales, n, w_layout=W_SLAB128, bias=None, out_dtype=None,
-                     out=None):
+def linear_blocks128(x_i8, x_block_scales, w_i8, w_block_scales, n, w_layout=W_SLAB128, bias=None, gate=None,
+                     residual=None, act=ACT_NONE, out_dtype=None, out=None):
     import torch
     m, k = x_i8.shape
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype or torch.float16, device=x_i8.device)
     _check(lib().b200_w8a8_linear_blocks128(_ptr(x_i8), _ptr(x_block_scales), _ptr(w_i8), w_layout, _ptr(w_block_scales),
-                                            _ptr(bias), _ptr(out), _dt(out), out.stride(0), m, k, n, _stream()),
-           "linear_blocks128")
+                                            _ptr(bias), _ptr(gate), _ptr(residual),
+                                            residual.stride(0) if residual is not None else 0, _ptr(out), _dt(out),
+                                            out.stride(0), m, k, n, act, _stream()), "linear_blocks128")
     return out
 
 

@@ -249,8 +249,9 @@ int b200_w8a8_quantize_blocks128(const void *x, int x_dtype, int64_t ldx, int8_t
 }
 
 int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, const int8_t *w_i8, int w_layout,
-                               const float *w_block_scales, const float *bias, void *y, int y_dtype, int64_t ldy, int m,
-                               int k, int n, void *stream) {
+                               const float *w_block_scales, const float *bias, const float *gate, const void *residual,
+                               int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
+                               void *stream) {
     if (status_check_entry()) return 1;
     Blocks128Args a = {};
     a.x = x_i8;
@@ -259,6 +260,10 @@ int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, 
     a.w_layout = w_layout;
     a.w_scales = w_block_scales;
     a.bias = bias;
+    a.gate = gate;
+    a.residual = residual;
+    a.ldr = ldr;
+    a.act = act;
     a.out = y;
     a.ldo = ldy;
     a.out_dtype = y_dtype;

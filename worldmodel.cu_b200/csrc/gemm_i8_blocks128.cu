@@ -6,7 +6,8 @@
 // scales before adding it to an fp32 accumulator:
 //     y = 0;  for kb in order:  y = fma(float(acc_kb[m, n]), sa[m / 128, kb] * sw[n / 128, kb], y)
 // (the scale pair's product rounded to fp32 first, then one fused multiply-add per K block, in fp32),
-// then + bias, then one rounding to the output type.
+// then the row/channel linear's epilogue (+ bias, activation, * gate, + residual) and one rounding to the
+// output type -- the reference's notes ask for exactly that: block scales inside the fused WorldDiT epilogues.
 // The reference tree holds no implementation of this rule (its authors ported a third-party kernel
 // out of tree), so parity here is against this library's own CPU restatement of the rule only.
 //
@@ -215,10 +216,25 @@ __global__ void __launch_bounds__(kBqThreads, 1)
                 uint32_t w[32];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) unpack2(acc[j], w[2 * j], w[2 * j + 1]);
-                if (p.bias) {
+                // + bias -> activation -> * gate -> + residual, the order and the separate roundings of the
+                // row/channel linear's epilogue; once per tile, so plain guarded accesses are cheap enough
+                if (p.bias || p.act != B200_ACT_NONE || p.gate || p.residual) {
+                    const int row = row0 + lane;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) w[j] = __float_as_uint(__fadd_rn(__uint_as_float(w[j]), __ldg(p.bias + col0 + j)));
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        if (col >= p.N) continue;
+                        float t = __uint_as_float(w[j]);
+                        if (p.bias) t = __fadd_rn(t, __ldg(p.bias + col));
+                        t = apply_act_rt(t, p.act);
+                        if (p.gate) t = __fmul_rn(t, __ldg(p.gate + col));
+                        if (p.residual && row < p.M) {
+                            const long long ri = (long long)row * p.ldr + col;
+                            if (OUT == B200_DT_F32) t = __fadd_rn(reinterpret_cast<const float *>(p.residual)[ri], t);
+                            else t = __fadd_rn(OutElem<Out16<OUT>::value>::load1(p.residual, ri), t);
+                        }
+                        w[j] = __float_as_uint(t);
+                    }
                 }
                 stage_and_store<OUT>(p, &tm_out, stage, w, lane, row0, col0, seq++);
             }
@@ -390,6 +406,10 @@ int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
     const int a_rows = a.m >= BM ? BM : ((a.m + 15) / 16) * 16;
     p.a_stage_bytes = a_rows * BK;
     p.bias = a.bias;
+    p.gate = a.gate;
+    p.residual = a.residual;
+    p.ldr = a.ldr;
+    p.act = a.act;
     p.out = a.out;
     p.ldo = a.ldo;
     p.out_dtype = a.out_dtype;
@@ -458,6 +478,8 @@ int linear_blocks128(const Blocks128Args &a, cudaStream_t stream) {
         return fail("linear_blocks128 writes fp32, fp16 or bf16");
     const size_t esz = a.out_dtype == B200_DT_F32 ? 4 : 2;
     if (!aligned16(a.x) || !aligned16(a.w)) return fail("linear_blocks128: codes must be 16-byte aligned");
+    if (a.act != B200_ACT_NONE && a.act != B200_ACT_SILU && a.act != B200_ACT_GELU_TANH) return fail("unknown activation %d", a.act);
+    if (a.residual && a.ldr < a.n) return fail("linear_blocks128: residual row stride %lld below N=%d", a.ldr, a.n);
     if (a.ldo < a.n || !aligned16(a.out) || ((size_t)a.ldo * esz) % 16 != 0)
         return fail("linear_blocks128: y must be 16-byte aligned with 16-byte aligned rows (ldo=%lld)", a.ldo);
     switch (a.out_dtype) {

@@ -163,6 +163,10 @@ struct Blocks128Args {
     int w_layout;
     const float *w_scales;   // [ceil(n / 128)][k / 128]
     const float *bias;       // [n], nullable
+    const float *gate;       // [n], nullable
+    const void *residual;    // [m, ldr] in the output type, nullable
+    long long ldr;
+    int act;
     void *out;               // [m, ldo]
     long long ldo;
     int out_dtype;           // fp32, fp16 or bf16
