@@ -80,6 +80,33 @@ def test_block_quantizer_rejects_bad_shapes(pkg):
         pkg.quantize_blocks128(torch.zeros(16, 130, device=DEV, dtype=torch.float16)[:, 1:129])
 
 
+def test_the_library_picks_the_wide_tile_when_it_fills_the_machine(pkg, ref):
+    """Unforced: 2048 x 6144 is 384 wide tiles (>= one per SM) -> 256-wide kernel; the same problem forced to 128-wide
+    tiles gives the same bits."""
+    m, k, n = 2048, 256, 6144
+    g = torch.Generator().manual_seed(31)
+    x = acts(m, k, 9)
+    w = torch.randn(n, k, generator=g) * 0.03
+    qx, sx = pkg.quantize_blocks128(x.to(DEV))
+    packed, sw = pkg.pack_weight_blocks128(w)
+    packed, sw = packed.to(DEV), sw.to(DEV)
+    y_auto = pkg.linear_blocks128(qx, sx, packed, sw, n=n)
+    pkg.lib().b200_w8a8_debug_force_plan(128, 0, 0)
+    try:
+        y_128 = pkg.linear_blocks128(qx, sx, packed, sw, n=n)
+    finally:
+        pkg.lib().b200_w8a8_debug_force_plan(0, 0, 0)
+    torch.cuda.synchronize()
+    qx_ref, sx_ref = ref.quantize_blocks128(x)
+    qw_ref, sw_ref = ref.quantize_blocks128(w)
+    want = ref.linear_blocks128(qx_ref, sx_ref, qw_ref, sw_ref, out_dtype=torch.float16)
+    assert torch.equal(y_auto.cpu(), want) and torch.equal(y_128.cpu(), want)
+
+
+test_the_library_picks_the_wide_tile_when_it_fills_the_machine = pytest.mark.gpu(
+    test_the_library_picks_the_wide_tile_when_it_fills_the_machine)
+
+
 CASES = [  # m, k, n, out dtype, layout, bias
     (128, 128, 128, torch.float32, 0, False),
     (100, 256, 200, torch.float16, 1, True),      # ragged rows and columns
@@ -91,9 +118,18 @@ CASES = [  # m, k, n, out dtype, layout, bias
 ]
 
 
+@pytest.fixture
+def tile_width(pkg, request):
+    """Forces the kernel's tile width (the library picks 256 only when that still gives every SM a tile)."""
+    pkg.lib().b200_w8a8_debug_force_plan(request.param, 0, 0)
+    yield request.param
+    pkg.lib().b200_w8a8_debug_force_plan(0, 0, 0)
+
+
 @pytest.mark.gpu
+@pytest.mark.parametrize("tile_width", [128, 256], indirect=True)
 @pytest.mark.parametrize("m,k,n,dtype,layout,with_bias", CASES)
-def test_blockwise_linear_bit_exact(pkg, ref, m, k, n, dtype, layout, with_bias):
+def test_blockwise_linear_bit_exact(pkg, ref, tile_width, m, k, n, dtype, layout, with_bias):
     g = torch.Generator().manual_seed(m + k + n)
     x = acts(m, k, m + n)
     w = torch.randn(n, k, generator=g) * 0.03
@@ -115,9 +151,10 @@ def test_blockwise_linear_bit_exact(pkg, ref, m, k, n, dtype, layout, with_bias)
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("tile_width", [128, 256], indirect=True)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("parts", ["res", "gate_res", "all"])
-def test_blockwise_linear_gate_and_residual_bit_exact(pkg, ref, dtype, parts):
+def test_blockwise_linear_gate_and_residual_bit_exact(pkg, ref, tile_width, dtype, parts):
     """The row/channel linear's epilogue on top of the blockwise accumulation: no transcendental, so exact."""
     m, k, n = 300, 512, 264
     g = torch.Generator().manual_seed(17)

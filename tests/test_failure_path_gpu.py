@@ -25,6 +25,7 @@ def short_waits(pkg):
     L.b200_w8a8_debug_set_wait_limit_ns(5_000_000)  # 5 ms instead of 2 s
     yield L
     L.b200_w8a8_debug_drop_operand_load(0)
+    L.b200_w8a8_debug_force_plan(0, 0, 0)
     L.b200_w8a8_debug_set_wait_limit_ns(0)
     torch.cuda.synchronize()
     pkg.poll_status()  # leave the word clean for the tests that follow
@@ -93,7 +94,8 @@ def test_row_quantizing_linear_times_out_cleanly(pkg, short_waits):
     assert pkg.poll_status() == 0
 
 
-def test_blockwise_linear_times_out_cleanly(pkg, ref, short_waits):
+@pytest.mark.parametrize("width", [128, 256])
+def test_blockwise_linear_times_out_cleanly(pkg, ref, short_waits, width):
     """The 128 x 128 blockwise kernel: its MMA issuer gives up, the sixteen epilogue warps and the producer see the
     abort flag and drain, tensor memory is returned, and the next call is exact."""
     L = short_waits
@@ -107,6 +109,7 @@ def test_blockwise_linear_times_out_cleanly(pkg, ref, short_waits):
     qx_ref, sx_ref = ref.quantize_blocks128(x)
     qw_ref, sw_ref = ref.quantize_blocks128(w)
     want = ref.linear_blocks128(qx_ref, sx_ref, qw_ref, sw_ref, out_dtype=torch.float16)
+    L.b200_w8a8_debug_force_plan(width, 0, 0)
     L.b200_w8a8_debug_drop_operand_load(1)
     pkg.linear_blocks128(qx, sx, packed, sw, n=n)      # launches; every CTA loses its first A tile
     torch.cuda.synchronize()
@@ -115,6 +118,7 @@ def test_blockwise_linear_times_out_cleanly(pkg, ref, short_waits):
     with pytest.raises(pkg.W8A8Error, match="gave up a bounded wait.*status 10[24]"):
         pkg.linear_blocks128(qx, sx, packed, sw, n=n)
     y = pkg.linear_blocks128(qx, sx, packed, sw, n=n)
+    L.b200_w8a8_debug_force_plan(0, 0, 0)
     torch.cuda.synchronize()
     assert pkg.poll_status() == 0
     assert torch.equal(y.cpu().view(torch.uint8), want.view(torch.uint8))

@@ -11,13 +11,13 @@
 // The reference tree holds no implementation of this rule (its authors ported a third-party kernel
 // out of tree), so parity here is against this library's own CPU restatement of the rule only.
 //
-// Kernel shape: a 128 x 128 output tile per persistent CTA, so one tile sees exactly one activation
-// block row and one weight block row and a K block's scale pair is a single number.  The tensor core
-// writes K block after K block into four 128-column accumulators of tensor memory in turn; sixteen
-// epilogue warps (four per SM sub-core, so the tensor-memory load of one hides behind the arithmetic
-// of the others) drain each one as soon as it is complete (`tcgen05.ld`, slot handed back at once)
-// and fold it into 32 fp32 registers per thread, while the next three K blocks are already running.
-// int32 -> fp32 is one integer add and one float subtract (|acc| <= 2^21 fits the mantissa of
+// Kernel shape: a 128 x 128 or 128 x 256 output tile per persistent CTA, so a warp's columns see exactly one
+// activation block row and one weight block row and a K block's scale pair is a single number per warp.  The
+// tensor core writes K block after K block into the accumulators of tensor memory in turn (four of 128 columns
+// or two of 256); eight epilogue warps drain each one as soon as it is complete (`tcgen05.ld` in chunks of 16
+// columns, the next chunk in flight while the current one is folded in; the slot is handed back when the last
+// chunk has landed) and accumulate in fp32 registers with two-wide instructions, while the next K blocks are
+// already running.  int32 -> fp32 is one integer add and one float subtract (|acc| <= 2^21 fits the mantissa of
 // 1.5 * 2^23), which keeps the conversion off the 16-lane conversion unit.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -27,22 +27,31 @@
 namespace b200 {
 namespace {
 
-constexpr int BQ = 128;                              // block edge = tile edge
-constexpr int kBqStageBytes = BM * BK + BQ * BK;     // 16 KB of A + 16 KB of W
-constexpr int kBqStages = 5;
-constexpr int kBqEpilogueWarps = 16;                 // 32 rows x 32 columns of the tile each
+constexpr int BQ = 128;                   // block edge
+constexpr int kBqEpilogueWarps = 8;       // two per tensor-memory sub-partition, half of the tile's columns each
 constexpr int kBqThreads = 64 + 32 * kBqEpilogueWarps;
-constexpr int kBqStagingBytes = kBqEpilogueWarps * kStagingPerWarp;
-constexpr int kBqSlots = 4;                          // K-block accumulators in tensor memory
-constexpr int kBqTmemCols = kBqSlots * BQ;           // all 512 columns
-constexpr int kBqBarBytes = (2 * kBqStages + kBqSlots) * 8 + 16;
-constexpr int kBqSmemBytes = kBqStages * kBqStageBytes + kBqStagingBytes + kBqBarBytes + 1024;
-static_assert(kBqSmemBytes <= 227 * 1024, "shared memory of the blockwise GEMM");
+constexpr int kBqStagePerWarp = 2048;     // one 32-row x 64-byte block of output per warp
+constexpr int kBqStagingBytes = kBqEpilogueWarps * kBqStagePerWarp;
 
-// Two fp32 values in one 64-bit register and the two-wide add / fused multiply-add on them: half the
-// instructions of the scalar forms, each half rounded like the scalar instruction.  (A two-wide multiply
-// followed by a two-wide add is not an alternative where separate roundings are wanted: the assembler
-// merges the pair into the fused form even when both carry an explicit rounding mode.)
+// BN = 128: one weight block per tile (more tiles: small problems); BN = 256: two weight blocks per tile, the
+// operand pipeline of the row/channel kernel's widest tile (half the A traffic and half the copies per unit of
+// work), chosen whenever it still fills the machine.
+template <int BN>
+struct BqCfg {
+    static constexpr int kStageBytes = BM * BK + BN * BK;
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kSlots = 512 / BN;                      // K-block accumulators: all 512 columns
+    static constexpr int kColsPerWarp = BN / 2;                  // 64 or 128: within one weight block
+    static constexpr int kChunks = kColsPerWarp / 32;            // output blocks of 32 columns per warp
+    static constexpr int kBarBytes = (2 * kStages + kSlots) * 8 + 16;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBqStagingBytes + kBarBytes + 1024;
+};
+static_assert(BqCfg<128>::kSmemBytes <= 227 * 1024 && BqCfg<256>::kSmemBytes <= 227 * 1024, "shared memory");
+
+// Two fp32 values in one 64-bit register and the two-wide fused multiply-add on them: half the instructions of
+// the scalar form, each half rounded like the scalar instruction.  (A two-wide multiply followed by a two-wide
+// add is not an alternative where separate roundings are wanted: the assembler merges the pair into the fused
+// form even when both carry an explicit rounding mode.)
 __device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
     uint64_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
@@ -62,26 +71,76 @@ __device__ __forceinline__ uint64_t fma2_rn(uint64_t a, uint64_t b, uint64_t c) 
     return d;
 }
 
+// 32 lanes x 16 consecutive 32-bit columns of tensor memory: thread t of the warp receives lane (base + t).
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 struct BlocksParams {
-    GemmParams g;            // shape, raster, output, bias, wait controls
+    GemmParams g;            // shape, raster, output, epilogue inputs, wait controls
     const float *a_scales;   // [ceil(M / 128)][K / 128]
     const float *w_scales;   // [ceil(N / 128)][K / 128]
+    int w_scale_rows;        // ceil(N / 128)
 };
 
+// One 32-row x 32-column block of the output: every thread writes its row into the warp's swizzled 2 KB staging
+// block, lane 0 hands it to the TMA store engine (which clips at the M / N edges).  A 32-bit block goes as two
+// halves of 16 columns through the same staging block.  Once per tile, so the stores are not overlapped.
 template <int OUT>
+__device__ __forceinline__ void store_block32(const CUtensorMap *tm_out, uint8_t *buf, const uint32_t (&w)[32], int lane,
+                                              int row0, int col0) {
+    constexpr bool k32 = OUT == B200_DT_F32;
+    uint8_t *rowp = buf + lane * 64;
+#pragma unroll
+    for (int h = 0; h < (k32 ? 2 : 1); ++h) {
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint4 val;
+            if (k32) {
+                val = make_uint4(w[16 * h + 4 * c], w[16 * h + 4 * c + 1], w[16 * h + 4 * c + 2], w[16 * h + 4 * c + 3]);
+            } else {
+                constexpr int O = Out16<OUT>::value;
+                val = make_uint4(OutElem<O>::pack(__uint_as_float(w[8 * c + 0]), __uint_as_float(w[8 * c + 1])),
+                                 OutElem<O>::pack(__uint_as_float(w[8 * c + 2]), __uint_as_float(w[8 * c + 3])),
+                                 OutElem<O>::pack(__uint_as_float(w[8 * c + 4]), __uint_as_float(w[8 * c + 5])),
+                                 OutElem<O>::pack(__uint_as_float(w[8 * c + 6]), __uint_as_float(w[8 * c + 7])));
+            }
+            *reinterpret_cast<uint4 *>(rowp + ((c ^ ((lane >> 1) & 3)) << 4)) = val;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tm_out),
+                         "r"(col0 + (k32 ? 16 * h : 0)), "r"(row0), "r"(smem_u32(buf))
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+}
+
+template <int OUT, int BN>
 __global__ void __launch_bounds__(kBqThreads, 1)
     gemm_i8_blocks128_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                              const __grid_constant__ CUtensorMap tm_out, const BlocksParams bp) {
+    using C = BqCfg<BN>;
     const GemmParams &p = bp.g;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *staging = smem + kBqStages * kBqStageBytes;
+    uint8_t *staging = smem + C::kStages * C::kStageBytes;
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(staging + kBqStagingBytes);
     // done[s]: the MMAs that read stage s have completed.  One commit per K block serves two waiters: the
     // producer (the stage may be refilled) and the epilogue warps (the K block's accumulator is complete).
-    uint64_t *bar_done = bar_full + kBqStages;
-    uint64_t *bar_tempty = bar_done + kBqStages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + kBqSlots);
+    uint64_t *bar_done = bar_full + C::kStages;
+    uint64_t *bar_tempty = bar_done + C::kStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_tempty + C::kSlots);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const WaitCtx wctx{abort_flag, p.status, p.wait_limit_ns};
 
@@ -90,11 +149,11 @@ __global__ void __launch_bounds__(kBqThreads, 1)
 
     pdl_trigger();
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kBqStages; ++s) {
+        for (int s = 0; s < C::kStages; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_done[s], 1);
         }
-        for (int b = 0; b < kBqSlots; ++b) mbar_init(&bar_tempty[b], kBqEpilogueWarps);
+        for (int b = 0; b < C::kSlots; ++b) mbar_init(&bar_tempty[b], kBqEpilogueWarps);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
@@ -102,7 +161,7 @@ __global__ void __launch_bounds__(kBqThreads, 1)
         tma_prefetch_desc(&tm_out);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, kBqTmemCols);
+        tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -122,100 +181,118 @@ __global__ void __launch_bounds__(kBqThreads, 1)
                 for (int kb = 0; kb < p.num_k_blocks; ++kb) {
                     ok = mbar_wait_bounded(&bar_done[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
                     if (!ok) break;
-                    uint8_t *sa = smem + s * kBqStageBytes;
-                    mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(p.a_stage_bytes + BQ * BK));
+                    uint8_t *sa = smem + s * C::kStageBytes;
+                    mbar_arrive_expect_tx(&bar_full[s], (uint32_t)(p.a_stage_bytes + BN * BK));
                     // test aid: leaving out the very first A tile makes the MMA issuer's wait run out
                     const bool drop = p.debug_drop_a_load && tile == (int)blockIdx.x && kb == 0;
                     if (!drop) tma_load_3d(sa, &tm_a, &bar_full[s], kb * BK, m_blk * BM, 0);
-                    tma_load_3d(sa + BM * BK, &tm_b, &bar_full[s], kb * p.b_kx, n_blk * BQ, kb * p.b_kz);
-                    if (++s == kBqStages) { s = 0; ph ^= 1u; }
+                    tma_load_3d(sa + BM * BK, &tm_b, &bar_full[s], kb * p.b_kx, n_blk * BN, kb * p.b_kz);
+                    if (++s == C::kStages) { s = 0; ph ^= 1u; }
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_i8(BM, BQ);
+            constexpr uint32_t idesc = umma_idesc_i8(BM, BN);
             int s = 0;
             uint32_t ph = 0;
-            uint32_t g = 0;  // K blocks issued so far by this CTA: slot g % 4, use number g / 4
+            uint32_t g = 0;  // K blocks issued so far by this CTA: slot g % kSlots, use number g / kSlots
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
                 for (int kb = 0; kb < p.num_k_blocks; ++kb, ++g) {
-                    const uint32_t slot = g & (kBqSlots - 1);
-                    const uint32_t use = (g / kBqSlots) & 1u;
+                    const uint32_t slot = g & (C::kSlots - 1);
+                    const uint32_t use = (g / C::kSlots) & 1u;
                     ok = mbar_wait_bounded(&bar_tempty[slot], use ^ 1u, wctx, KS_TIMEOUT_TMEM_EMPTY);
                     if (!ok) break;
                     ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_u32(smem + s * kBqStageBytes);
+                    const uint32_t sa = smem_u32(smem + s * C::kStageBytes);
                     const uint64_t da = umma_smem_desc_k128(sa);
                     const uint64_t db = umma_smem_desc_k128(sa + (uint32_t)(BM * BK));
-                    const uint32_t d_tmem = tmem_base + slot * (uint32_t)BQ;
+                    const uint32_t d_tmem = tmem_base + slot * (uint32_t)BN;
 #pragma unroll
                     for (int j = 0; j < BK / 32; ++j)
                         umma_i8(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc, (uint32_t)(j != 0));
                     umma_commit(&bar_done[s]);  // the stage may be refilled, and this K block's sums are complete
-                    if (++s == kBqStages) { s = 0; ph ^= 1u; }
+                    if (++s == C::kStages) { s = 0; ph ^= 1u; }
                 }
             }
         }
         __syncwarp();
     } else {
         const int ew = warp - 2;
-        const int sub = warp & 3;   // TMEM sub-partition this warp may read
-        const int quarter = ew >> 2;  // which 32 of the tile's 128 columns
-        uint8_t *stage = staging + ew * kStagingPerWarp;
+        const int sub = warp & 3;     // TMEM sub-partition this warp may read
+        const int part = ew >> 2;     // which kColsPerWarp of the tile's columns
+        uint8_t *stage = staging + ew * kBqStagePerWarp;
         pdl_wait();  // the activation block scales come from the kernel before this one
         uint32_t g = 0;
         int s = 0;        // the stage whose `done` barrier announces K block g
         uint32_t ph = 0;
-        int seq = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
             int m_blk, n_blk;
             decode_tile(p, tile, m_blk, n_blk);
+            const int colbase = n_blk * BN + part * C::kColsPerWarp;
+            // this warp's columns lie in one weight block; beyond the last block there is nothing to scale or store
+            const int w_blk = min(colbase / BQ, bp.w_scale_rows - 1);
             const float *sa_row = bp.a_scales + (long long)m_blk * p.num_k_blocks;
-            const float *sw_row = bp.w_scales + (long long)n_blk * p.num_k_blocks;
-            uint64_t acc[16];  // fp32 pairs (columns 2j, 2j+1): the arithmetic below is two-wide
+            const float *sw_row = bp.w_scales + (long long)w_blk * p.num_k_blocks;
+            uint64_t acc[C::kChunks][16];  // fp32 pairs (columns 2j, 2j+1): the arithmetic below is two-wide
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] = 0ull;
+            for (int c = 0; c < C::kChunks; ++c)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c][j] = 0ull;
             float f_next = __fmul_rn(__ldg(sa_row), __ldg(sw_row));
 #pragma unroll 1
             for (int kb = 0; kb < p.num_k_blocks; ++kb, ++g) {
-                const uint32_t slot = g & (kBqSlots - 1);
+                const uint32_t slot = g & (C::kSlots - 1);
                 const float f = f_next;
                 if (kb + 1 < p.num_k_blocks) f_next = __fmul_rn(__ldg(sa_row + kb + 1), __ldg(sw_row + kb + 1));
                 ok = mbar_wait_bounded(&bar_done[s], ph, wctx, KS_TIMEOUT_TMEM_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                if (++s == kBqStages) { s = 0; ph ^= 1u; }
+                if (++s == C::kStages) { s = 0; ph ^= 1u; }
                 tc_fence_after_sync();
-                const uint32_t taddr =
-                    tmem_base + ((uint32_t)(sub * 32) << 16) + slot * (uint32_t)BQ + (uint32_t)(quarter * 32);
-                uint32_t r0[32];
-                tmem_ld_32x32(taddr, r0);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_tempty[slot]);  // the tensor core may overwrite the slot
-                // float(acc) exactly: 1.5 * 2^23 + acc is representable for |acc| <= 2^22 (here <= 2^21)
+                const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + slot * (uint32_t)BN +
+                                       (uint32_t)(part * C::kColsPerWarp);
                 const uint64_t ff = pack2(__float_as_uint(f), __float_as_uint(f));
-                const uint64_t unbias = pack2(__float_as_uint(-12582912.0f), __float_as_uint(-12582912.0f));
+                // 16 columns per tensor-memory load, two register buffers: the load of chunk c+1 is in flight while
+                // chunk c is folded in; the slot goes back to the tensor core as soon as the last load has landed
+                constexpr int kLoads = C::kColsPerWarp / 16;
+                uint32_t ra[16], rb[16];
+                tmem_ld_32x16(taddr, ra);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint64_t v = add2_rn(pack2(r0[2 * j] + 0x4B400000u, r0[2 * j + 1] + 0x4B400000u), unbias);
-                    acc[j] = fma2_rn(v, ff, acc[j]);
+                for (int c = 0; c < kLoads; ++c) {
+                    tmem_ld_wait();
+                    if (c + 1 < kLoads) {
+                        tmem_ld_32x16(taddr + (uint32_t)(16 * (c + 1)), (c & 1) ? ra : rb);
+                    } else {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_tempty[slot]);
+                    }
+                    const uint32_t(&r0)[16] = (c & 1) ? rb : ra;
+                    // float(acc) exactly: 1.5 * 2^23 + acc is representable for |acc| <= 2^22 (here <= 2^21)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint64_t &dst = acc[c / 2][(c & 1) * 8 + j];
+                        const uint64_t v = add2_rn(pack2(r0[2 * j] + 0x4B400000u, r0[2 * j + 1] + 0x4B400000u),
+                                                   pack2(__float_as_uint(-12582912.0f), __float_as_uint(-12582912.0f)));
+                        dst = fma2_rn(v, ff, dst);
+                    }
                 }
             }
             if (!ok) break;
             const int row0 = m_blk * BM + sub * 32;
-            const int col0 = n_blk * BQ + quarter * 32;
-            if (col0 < p.N) {  // warp-uniform
+#pragma unroll
+            for (int c = 0; c < C::kChunks; ++c) {
+                const int col0 = colbase + 32 * c;
+                if (col0 >= p.N) break;  // warp-uniform
                 uint32_t w[32];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) unpack2(acc[j], w[2 * j], w[2 * j + 1]);
+                for (int j = 0; j < 16; ++j) unpack2(acc[c][j], w[2 * j], w[2 * j + 1]);
                 // + bias -> activation -> * gate -> + residual, the order and the separate roundings of the
                 // row/channel linear's epilogue; once per tile, so plain guarded accesses are cheap enough
                 if (p.bias || p.act != B200_ACT_NONE || p.gate || p.residual) {
@@ -236,7 +313,7 @@ __global__ void __launch_bounds__(kBqThreads, 1)
                         w[j] = __float_as_uint(t);
                     }
                 }
-                stage_and_store<OUT>(p, &tm_out, stage, w, lane, row0, col0, seq++);
+                store_block32<OUT>(&tm_out, stage, w, lane, row0, col0);
             }
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -254,7 +331,7 @@ __global__ void __launch_bounds__(kBqThreads, 1)
     }
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, kBqTmemCols);
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -375,20 +452,22 @@ __global__ void __launch_bounds__(512, 2) quant_blocks128_kernel(const T *__rest
 }
 
 struct BlocksDeviceInfo {
-    bool attr_set[3] = {};
+    bool attr_set[3][2] = {};
 };
 BlocksDeviceInfo &blocks_device_info(int dev) {
     static BlocksDeviceInfo info[64];
     return info[dev & 63];
 }
 
-template <int OUT>
+template <int OUT, int BN>
 int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
+    using C = BqCfg<BN>;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return fail("cudaGetDevice failed");
     BlocksDeviceInfo &di = blocks_device_info(dev);
     constexpr int oi = OUT == B200_DT_F32 ? 0 : (OUT == B200_DT_F16 ? 1 : 2);
-    if (ensure_smem_attr(di.attr_set[oi], gemm_i8_blocks128_kernel<OUT>, kBqSmemBytes, "gemm_i8_blocks128_kernel"))
+    if (ensure_smem_attr(di.attr_set[oi][BN == 256], gemm_i8_blocks128_kernel<OUT, BN>, C::kSmemBytes,
+                         "gemm_i8_blocks128_kernel"))
         return 1;
     BlocksParams bp;
     memset(&bp, 0, sizeof(bp));
@@ -397,7 +476,7 @@ int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
     p.N = a.n;
     p.K = a.k;
     p.num_m_blocks = (a.m + BM - 1) / BM;
-    p.num_n_blocks = (a.n + BQ - 1) / BQ;
+    p.num_n_blocks = (a.n + BN - 1) / BN;
     p.num_tiles = p.num_m_blocks * p.num_n_blocks;
     p.num_k_blocks = a.k / BK;
     p.group_m = 32;
@@ -419,16 +498,17 @@ int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
     p.debug_drop_a_load = take_debug_drop();
     bp.a_scales = a.x_scales;
     bp.w_scales = a.w_scales;
+    bp.w_scale_rows = (a.n + BQ - 1) / BQ;
     CUtensorMap tm_a, tm_b, tm_out;
     if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m,
                  (uint32_t)a_rows))
         return 1;
     if (a.w_layout == B200_W_SLAB128) {
-        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, BQ)) return 1;
+        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, BN)) return 1;
         p.b_kx = 0;
         p.b_kz = 1;
     } else {
-        if (make_map(&tm_b, a.w, (uint64_t)a.k, (uint64_t)a.n, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.n, BQ))
+        if (make_map(&tm_b, a.w, (uint64_t)a.k, (uint64_t)a.n, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.n, BN))
             return 1;
         p.b_kx = BK;
         p.b_kz = 0;
@@ -436,10 +516,19 @@ int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
     if (make_out_map(&tm_out, a.out, a.out_dtype, (uint64_t)a.n, (uint64_t)a.m, (uint64_t)a.ldo)) return 1;
     const int sms = device_sms();
     const int grid = p.num_tiles < sms ? p.num_tiles : sms;
-    cudaError_t le = launch_kernel(gemm_i8_blocks128_kernel<OUT>, dim3((unsigned)grid), dim3(kBqThreads),
-                                   (size_t)kBqSmemBytes, stream, tm_a, tm_b, tm_out, bp);
+    cudaError_t le = launch_kernel(gemm_i8_blocks128_kernel<OUT, BN>, dim3((unsigned)grid), dim3(kBqThreads),
+                                   (size_t)C::kSmemBytes, stream, tm_a, tm_b, tm_out, bp);
     if (le != cudaSuccess) return fail("launching gemm_i8_blocks128: %s", cudaGetErrorString(le));
     return check_launch("gemm_i8_blocks128");
+}
+
+// 256-wide tiles whenever they still give every SM a tile (or when forced for a test), else 128-wide ones.
+template <int OUT>
+int launch_blocks128_any(const Blocks128Args &a, cudaStream_t stream) {
+    const int forced = gemm_forced_tile_width();
+    const long long wide_tiles = (long long)((a.m + BM - 1) / BM) * ((a.n + 255) / 256);
+    const bool wide = forced == 256 || (forced != 128 && forced != 64 && wide_tiles >= device_sms());
+    return wide ? launch_blocks128<OUT, 256>(a, stream) : launch_blocks128<OUT, 128>(a, stream);
 }
 
 }  // namespace
@@ -483,9 +572,9 @@ int linear_blocks128(const Blocks128Args &a, cudaStream_t stream) {
     if (a.ldo < a.n || !aligned16(a.out) || ((size_t)a.ldo * esz) % 16 != 0)
         return fail("linear_blocks128: y must be 16-byte aligned with 16-byte aligned rows (ldo=%lld)", a.ldo);
     switch (a.out_dtype) {
-        case B200_DT_F32: return launch_blocks128<B200_DT_F32>(a, stream);
-        case B200_DT_F16: return launch_blocks128<B200_DT_F16>(a, stream);
-        default: return launch_blocks128<B200_DT_BF16>(a, stream);
+        case B200_DT_F32: return launch_blocks128_any<B200_DT_F32>(a, stream);
+        case B200_DT_F16: return launch_blocks128_any<B200_DT_F16>(a, stream);
+        default: return launch_blocks128_any<B200_DT_BF16>(a, stream);
     }
 }
 

@@ -1140,6 +1140,7 @@ void gemm_force_plan(int bn, int splits, int mode) {
     g_force_splits = splits;
     g_force_mode = mode;
 }
+int gemm_forced_tile_width() { return g_force_bn; }
 void gemm_set_pair_mode(int mode) { g_pair_mode = mode; }
 void gemm_set_one_slab_stages(int on) { g_one_slab_stages = on != 0; }
 void gemm_set_trace_buffer(unsigned long long *dev_buf) { g_trace = dev_buf; }

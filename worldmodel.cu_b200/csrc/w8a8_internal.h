@@ -196,6 +196,7 @@ void gemm_set_one_slab_stages(int on);
 void gemm_set_trace_buffer(unsigned long long *dev_buf);
 unsigned long long *gemm_trace_buffer();
 void gemm_force_plan(int bn, int splits, int mode);
+int gemm_forced_tile_width();  // 0 unless a test forced one
 
 // ---- mma_rate.cu
 int mma_issue_rate(int slabs_per_cta, double *tera_ops_per_s);
