@@ -796,7 +796,7 @@ def run_blockwise(pkg, stream, rows=8192, n_weights=8):
 
         def quant_blocks():
             for _ in wq:
-                pkg.lib().b200_w8a8_quantize_blocks128(x.data_ptr(), pkg.DT_F16, k, qb.data_ptr(), k, sb.data_ptr(), rows, k,
+                pkg.lib().b200_w8a8_quantize_blocks128(x.data_ptr(), pkg.DT_F16, k, qb.data_ptr(), k, sb.data_ptr(), rows, k, 128,
                                                        torch.cuda.current_stream().cuda_stream)
 
         def quant_rows():

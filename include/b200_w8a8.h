@@ -300,16 +300,19 @@ int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, in
  *     v = 0;  for kb in order:  v = fma(float(acc_kb[r, c]), xs[r / 128][kb] * ws[c / 128][kb], v)
  * in fp32 (the scale product rounded first, one fused multiply-add per K block), followed by the epilogue
  * of b200_w8a8_linear, y = store(residual + gate * act(v + bias)) with bias / gate / residual nullable --
- * block scales inside the fused epilogues are what the reference's notes (:356) ask of this variant.  Scale arrays are [ceil(rows / 128)][K / 128], row-major.
+ * block scales inside the fused epilogues are what the reference's notes (:356) ask of this variant.
+ * block_rows / x_block_rows = 128 is that rule; 1 gives every token row its own scale per K block (1 x 128
+ * activation groups, scales [rows][K / 128]; weights stay 128 x 128), for inputs whose rows differ in range:
+ * rows that share a 128-row block with an outlier row otherwise lose their resolution.  Scale arrays are [ceil(rows / 128)][K / 128], row-major.
  * K must be a multiple of 128; code and y buffers 16-byte aligned with 16-byte aligned rows. */
 int b200_w8a8_quantize_blocks128(const void *x, int x_dtype, int64_t ldx, int8_t *q, int64_t ldq, float *block_scales,
-                                 int rows, int cols, void *stream);
+                                 int rows, int cols, int block_rows, void *stream);
 int b200_w8a8_pack_weight_blocks128_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
                                          float *block_scales_host, int threads);
 int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, const int8_t *w_i8, int w_layout,
                                const float *w_block_scales, const float *bias, const float *gate, const void *residual,
                                int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
-                               void *stream);
+                               int x_block_rows, void *stream);
 
 /* ---- the linear stack (host-side driver above the operators) ----------------------- */
 

@@ -354,6 +354,17 @@ def quantize_blocks128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return q.view(rb * 128, cols)[:rows].contiguous(), scale
 
 
+def quantize_row_blocks128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same rule on 1 x 128 groups: one scale per row and 128-wide K block.  Returns (int8 [R, C], fp32 [R, C/128])."""
+    assert x.ndim == 2 and x.shape[1] % 128 == 0
+    x = x.to(torch.float32)
+    rows, cols = x.shape
+    groups = x.view(rows, cols // 128, 128)
+    scale = torch.clamp(groups.abs().amax(dim=2), min=1e-8) / 128.0
+    q = torch.round(groups / scale[:, :, None]).clamp(-128, 127).to(torch.int8)
+    return q.view(rows, cols).contiguous(), scale
+
+
 def fma_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
     """Correctly rounded fp32 fused multiply-add a * b + c for fp32 inputs whose product is exact in fp64 (here a is
     an integer of at most 22 bits).  The product is formed exactly in fp64; adding c rounds once to fp64 and the
@@ -377,7 +388,7 @@ def fma_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
 
 
 def linear_blocks128(qx, sx, qw, sw, bias=None, out_dtype=torch.float16, act=ACT_NONE, gate=None,
-                     residual=None) -> torch.Tensor:
+                     residual=None, x_scale_per_row=False) -> torch.Tensor:
     """y = 0; for every K block in order y = fma(float(acc_kb), sx[r/128, kb] * sw[c/128, kb], y) in fp32 (the scale
     product rounded to fp32 first), then the epilogue of `epilogue_f32` (+ bias, activation, * gate, + residual) and one
     rounding to the output type.  acc_kb is the exact int32
@@ -385,7 +396,7 @@ def linear_blocks128(qx, sx, qw, sw, bias=None, out_dtype=torch.float16, act=ACT
     m, k = qx.shape
     n = qw.shape[0]
     assert k % 128 == 0 and qw.shape[1] == k
-    rows = torch.arange(m) // 128
+    rows = torch.arange(m) if x_scale_per_row else torch.arange(m) // 128
     cols = torch.arange(n) // 128
     y = torch.zeros(m, n, dtype=torch.float32)
     for kb in range(k // 128):

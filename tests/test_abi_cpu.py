@@ -120,3 +120,45 @@ def test_reference_operator_library_exports_the_eight_w8a8_operators():
                   "dequant_silu_quantize_rows_i8", "dequant_gated_residual_f32", "dequant_add_residual_f32",
                   "qkv_fused_rms_rope_i32_dequant"):
         assert callable(getattr(lib, short))
+
+
+def test_ctypes_prototypes_match_the_header_parameter_by_parameter(pkg):
+    """ctypes does not complain about a call with one argument too many or too few, so the Python prototype table
+    is checked against the C declarations: same number of parameters, each of the same class (pointer, 32-bit
+    integer, 64-bit integer / size, float, double)."""
+    import ctypes
+    text = (ROOT / "include" / "b200_w8a8.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    decls = re.findall(r"\b(b200_w8a8_\w+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S)
+    assert len(decls) >= 50
+
+    def c_kind(param):
+        p = " ".join(param.split())
+        if p in ("void", ""):
+            return None
+        if "*" in p:
+            return "ptr"
+        if "int64_t" in p or "size_t" in p or "unsigned long long" in p:
+            return "i64"
+        if "double" in p:
+            return "f64"
+        if "float" in p:
+            return "f32"
+        assert re.search(r"\bint\b", p), f"unclassified parameter `{p}`"
+        return "i32"
+
+    def py_kind(t):
+        if t in (ctypes.c_int64, ctypes.c_size_t, ctypes.c_ulonglong, ctypes.c_uint64):
+            return "i64"
+        if t is ctypes.c_int:
+            return "i32"
+        if t is ctypes.c_float:
+            return "f32"
+        if t is ctypes.c_double:
+            return "f64"
+        return "ptr"  # c_void_p, c_char_p, POINTER(...)
+
+    for name, params in decls:
+        want = [k for k in (c_kind(x) for x in params.split(",")) if k is not None]
+        got = [py_kind(t) for t in pkg._PROTOTYPES[name][1]]
+        assert want == got, f"{name}: header {want}, Python table {got}"

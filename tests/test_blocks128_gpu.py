@@ -78,6 +78,8 @@ def test_block_quantizer_rejects_bad_shapes(pkg):
         pkg.quantize_blocks128(torch.zeros(16, 96, device=DEV))
     with pytest.raises(pkg.W8A8Error, match="aligned"):
         pkg.quantize_blocks128(torch.zeros(16, 130, device=DEV, dtype=torch.float16)[:, 1:129])
+    with pytest.raises(pkg.W8A8Error, match="128 or 1"):
+        pkg.quantize_blocks128(torch.zeros(16, 128, device=DEV), block_rows=64)
 
 
 def test_the_library_picks_the_wide_tile_when_it_fills_the_machine(pkg, ref):
@@ -205,6 +207,71 @@ def test_blockwise_linear_activation_then_block_requantization(pkg, ref, act):
     assert torch.equal(qh.cpu(), qh_ref) and torch.equal(sh.cpu(), sh_ref)
     want = ref.linear_blocks128(qh_ref, sh_ref, q2, t2, residual=res, out_dtype=torch.float32)
     assert torch.equal(y.cpu().view(torch.uint8), want.view(torch.uint8))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(1, 128), (130, 256), (1000, 2048)])
+def test_row_group_quantizer_bit_exact(pkg, ref, rows, cols, dtype):
+    """block_rows = 1: every token row keeps its own scale per K block."""
+    x = acts(rows, cols, rows + cols + 1, dtype)
+    q, s = pkg.quantize_blocks128(x.to(DEV), block_rows=1)
+    q_ref, s_ref = ref.quantize_row_blocks128(x)
+    assert s.shape == (rows, cols // 128)
+    assert torch.equal(s.cpu().view(torch.int32), s_ref.view(torch.int32))
+    assert torch.equal(q.cpu(), q_ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tile_width", [128, 256], indirect=True)
+@pytest.mark.parametrize("m,k,n,dtype", [(100, 256, 200, torch.float16), (300, 1024, 520, torch.float32),
+                                         (1100, 512, 1280, torch.bfloat16)])
+def test_blockwise_linear_with_row_groups_bit_exact(pkg, ref, tile_width, m, k, n, dtype):
+    g = torch.Generator().manual_seed(m + n)
+    x = acts(m, k, m)
+    x[::7] *= 25.0                       # token rows of very different range
+    w = torch.randn(n, k, generator=g) * 0.03
+    bias = torch.randn(n, generator=g) * 0.1
+    res = torch.randn(m, n, generator=g).to(dtype)
+    qx, sx = pkg.quantize_blocks128(x.to(DEV), block_rows=1)
+    packed, sw = pkg.pack_weight_blocks128(w)
+    y = pkg.linear_blocks128(qx, sx, packed.to(DEV), sw.to(DEV), n=n, bias=bias.to(DEV), residual=res.to(DEV),
+                             out_dtype=dtype, x_block_rows=1)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    qx_ref, sx_ref = ref.quantize_row_blocks128(x)
+    qw_ref, sw_ref = ref.quantize_blocks128(w)
+    want = ref.linear_blocks128(qx_ref, sx_ref, qw_ref, sw_ref, bias=bias, residual=res, out_dtype=dtype,
+                                x_scale_per_row=True)
+    assert torch.equal(y.cpu().view(torch.uint8), want.view(torch.uint8))
+
+
+@pytest.mark.gpu
+def test_row_groups_keep_ordinary_rows_next_to_outlier_rows(pkg, ref):
+    """Every 64th token 20x larger: with 128 x 128 activation blocks the ordinary rows share a scale with an outlier
+    row and lose ~20 dB; with 1 x 128 groups they keep the row/channel rule's quality (and the K-block scales on top)."""
+    g = torch.Generator().manual_seed(8)
+    m, k, n = 512, 2048, 1024
+    x = torch.randn(m, k, generator=g)
+    x[::64] *= 20.0
+    w = torch.randn(n, k, generator=g) * 0.02
+    exact = (x.double() @ w.double().T).float()
+    packed, sw = pkg.pack_weight_blocks128(w)
+    packed, sw = packed.to(DEV), sw.to(DEV)
+    q2, s2 = pkg.quantize_blocks128(x.to(DEV))
+    y_blocks = pkg.linear_blocks128(q2, s2, packed, sw, n=n, out_dtype=torch.float32)
+    q1, s1 = pkg.quantize_blocks128(x.to(DEV), block_rows=1)
+    y_groups = pkg.linear_blocks128(q1, s1, packed, sw, n=n, out_dtype=torch.float32, x_block_rows=1)
+    qr, sr = pkg.quantize_rows(x.to(DEV))
+    pw, swr = pkg.pack_weight(w)
+    y_rows = pkg.linear(qr, sr, pw.to(DEV), swr.to(DEV), n=n, w_layout=pkg.W_SLAB128, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    ordinary = torch.ones(m, dtype=torch.bool)
+    ordinary[::64] = False
+    db = lambda y: ref.sqnr_db(exact[ordinary], y.cpu()[ordinary])
+    blocks, groups, rows = db(y_blocks), db(y_groups), db(y_rows)
+    assert groups > blocks + 10.0, (blocks, groups, rows)
+    assert groups > rows - 1.0, (blocks, groups, rows)
 
 
 @pytest.mark.gpu

@@ -73,9 +73,10 @@ _PROTOTYPES = {
     "b200_w8a8_packed_weight_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200_w8a8_pack_weight_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "b200_w8a8_pack_weight_blocks128_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
-    "b200_w8a8_quantize_blocks128": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p]),
+    "b200_w8a8_quantize_blocks128": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
+                                             c_void_p]),
     "b200_w8a8_linear_blocks128": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                           c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+                                           c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_stack_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]),
     "b200_w8a8_stack_destroy": (None, [c_void_p]),
     "b200_w8a8_stack_set_layer": (c_int, [c_void_p, c_int] + [c_void_p] * 8 + [c_int]),
@@ -369,20 +370,21 @@ def pack_weight_blocks128(w_f32_cpu, layout=W_SLAB128, threads=0):
     return packed, scales
 
 
-def quantize_blocks128(x):
+def quantize_blocks128(x, block_rows=128):
     """x: [rows, cols] CUDA tensor (fp32/fp16/bf16), cols % 128 == 0.  Returns (codes int8, block scales
-    [ceil(rows/128), cols/128])."""
+    [ceil(rows/128), cols/128]; with block_rows=1 one scale per row and K block, [rows, cols/128])."""
     import torch
     rows, cols = x.shape
     q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
-    s = torch.empty((rows + 127) // 128, max(cols // 128, 1), dtype=torch.float32, device=x.device)
-    _check(lib().b200_w8a8_quantize_blocks128(_ptr(x), _dt(x), x.stride(0), _ptr(q), cols, _ptr(s), rows, cols, _stream()),
-           "quantize_blocks128")
+    s = torch.empty(rows if block_rows == 1 else (rows + 127) // 128, max(cols // 128, 1), dtype=torch.float32,
+                    device=x.device)
+    _check(lib().b200_w8a8_quantize_blocks128(_ptr(x), _dt(x), x.stride(0), _ptr(q), cols, _ptr(s), rows, cols,
+                                              block_rows, _stream()), "quantize_blocks128")
     return q, s
 
 
 def linear_blocks128(x_i8, x_block_scales, w_i8, w_block_scales, n, w_layout=W_SLAB128, bias=None, gate=None,
-                     residual=None, act=ACT_NONE, out_dtype=None, out=None):
+                     residual=None, act=ACT_NONE, out_dtype=None, out=None, x_block_rows=128):
     import torch
     m, k = x_i8.shape
     if out is None:
@@ -390,7 +392,7 @@ def linear_blocks128(x_i8, x_block_scales, w_i8, w_block_scales, n, w_layout=W_S
     _check(lib().b200_w8a8_linear_blocks128(_ptr(x_i8), _ptr(x_block_scales), _ptr(w_i8), w_layout, _ptr(w_block_scales),
                                             _ptr(bias), _ptr(gate), _ptr(residual),
                                             residual.stride(0) if residual is not None else 0, _ptr(out), _dt(out),
-                                            out.stride(0), m, k, n, act, _stream()), "linear_blocks128")
+                                            out.stride(0), m, k, n, act, x_block_rows, _stream()), "linear_blocks128")
     return out
 
 

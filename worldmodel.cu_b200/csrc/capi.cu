@@ -243,19 +243,22 @@ int b200_w8a8_pack_weight_blocks128_host(const float *w_host, int n, int k, int 
 }
 
 int b200_w8a8_quantize_blocks128(const void *x, int x_dtype, int64_t ldx, int8_t *q, int64_t ldq, float *block_scales,
-                                 int rows, int cols, void *stream) {
+                                 int rows, int cols, int block_rows, void *stream) {
     if (status_check_entry()) return 1;
-    return quantize_blocks128(x, x_dtype, ldx, q, ldq, block_scales, rows, cols, as_stream(stream));
+    if (block_rows != 128 && block_rows != 1) return fail("quantize_blocks128: block_rows must be 128 or 1, got %d", block_rows);
+    return quantize_blocks128(x, x_dtype, ldx, q, ldq, block_scales, rows, cols, block_rows == 1, as_stream(stream));
 }
 
 int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, const int8_t *w_i8, int w_layout,
                                const float *w_block_scales, const float *bias, const float *gate, const void *residual,
                                int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,
-                               void *stream) {
+                               int x_block_rows, void *stream) {
     if (status_check_entry()) return 1;
+    if (x_block_rows != 128 && x_block_rows != 1) return fail("linear_blocks128: x_block_rows must be 128 or 1, got %d", x_block_rows);
     Blocks128Args a = {};
     a.x = x_i8;
     a.x_scales = x_block_scales;
+    a.x_scale_per_row = x_block_rows == 1;
     a.w = w_i8;
     a.w_layout = w_layout;
     a.w_scales = w_block_scales;

@@ -84,7 +84,8 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
 
 struct BlocksParams {
     GemmParams g;            // shape, raster, output, epilogue inputs, wait controls
-    const float *a_scales;   // [ceil(M / 128)][K / 128]
+    const float *a_scales;   // [ceil(M / 128)][K / 128], or [M][K / 128] when every token row has its own
+    int a_scale_per_row;     // 1: one activation scale per row and K block (1 x 128 groups)
     const float *w_scales;   // [ceil(N / 128)][K / 128]
     int w_scale_rows;        // ceil(N / 128)
 };
@@ -237,7 +238,9 @@ __global__ void __launch_bounds__(kBqThreads, 1)
             const int colbase = n_blk * BN + part * C::kColsPerWarp;
             // this warp's columns lie in one weight block; beyond the last block there is nothing to scale or store
             const int w_blk = min(colbase / BQ, bp.w_scale_rows - 1);
-            const float *sa_row = bp.a_scales + (long long)m_blk * p.num_k_blocks;
+            // the activation scale of this thread's row: shared by the 128-row block, or the row's own
+            const long long a_idx = bp.a_scale_per_row ? (long long)min(m_blk * BM + sub * 32 + lane, p.M - 1) : m_blk;
+            const float *sa_row = bp.a_scales + a_idx * p.num_k_blocks;
             const float *sw_row = bp.w_scales + (long long)w_blk * p.num_k_blocks;
             uint64_t acc[C::kChunks][16];  // fp32 pairs (columns 2j, 2j+1): the arithmetic below is two-wide
 #pragma unroll
@@ -403,7 +406,9 @@ struct Load32<__nv_bfloat16> {
 
 // One CTA of 512 threads per 128 x 128 block: four threads per row, 32 contiguous elements each, held in
 // registers between the block maximum and the codes, so the input is read once; two CTAs fit an SM.
-template <typename T>
+// PER_ROW: the same rule on 1 x 128 groups (every token row its own scale per K block, scales[rows][K / 128]): the four
+// threads of a row share their maximum with two shuffles and the block-wide reduction falls away.
+template <typename T, bool PER_ROW>
 __global__ void __launch_bounds__(512, 2) quant_blocks128_kernel(const T *__restrict__ x, long long ldx,
                                                                   int8_t *__restrict__ q, long long ldq,
                                                                   float *__restrict__ scales, int rows, int k_blocks) {
@@ -424,17 +429,26 @@ __global__ void __launch_bounds__(512, 2) quant_blocks128_kernel(const T *__rest
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    if (PER_ROW) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    } else {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = red[0];
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        amax = red[0];
 #pragma unroll
-    for (int i = 1; i < 16; ++i) amax = fmaxf(amax, red[i]);
+        for (int i = 1; i < 16; ++i) amax = fmaxf(amax, red[i]);
+    }
     BlockScale bs;
     bs.scale = __fmul_rn(fmaxf(amax, 1e-8f), 0.0078125f);  // / 128: exact, the result is a normal number
     bs.inv = bs.scale < 1e30f ? __frcp_rn(bs.scale) : 0.0f;
-    if (threadIdx.x == 0) scales[(long long)mb * k_blocks + kb] = bs.scale;
+    if (PER_ROW) {
+        if (live && (threadIdx.x & 3) == 0) scales[(long long)r * k_blocks + kb] = bs.scale;
+    } else if (threadIdx.x == 0) {
+        scales[(long long)mb * k_blocks + kb] = bs.scale;
+    }
     if (!live) return;
     uint4 *dst = reinterpret_cast<uint4 *>(q + (long long)r * ldq + c0);
 #pragma unroll
@@ -497,6 +511,7 @@ int launch_blocks128(const Blocks128Args &a, cudaStream_t stream) {
     p.wait_limit_ns = wait_limit_ns();
     p.debug_drop_a_load = take_debug_drop();
     bp.a_scales = a.x_scales;
+    bp.a_scale_per_row = a.x_scale_per_row ? 1 : 0;
     bp.w_scales = a.w_scales;
     bp.w_scale_rows = (a.n + BQ - 1) / BQ;
     CUtensorMap tm_a, tm_b, tm_out;
@@ -533,8 +548,22 @@ int launch_blocks128_any(const Blocks128Args &a, cudaStream_t stream) {
 
 }  // namespace
 
+template <bool PER_ROW>
+static cudaError_t launch_quant_blocks(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales,
+                                       int rows, int cols, cudaStream_t stream) {
+    const dim3 grid((unsigned)(cols / BQ), (unsigned)((rows + BQ - 1) / BQ));
+    if (in_dtype == B200_DT_F32)
+        return launch_kernel(quant_blocks128_kernel<float, PER_ROW>, grid, dim3(512), 0, stream, (const float *)x, ldx, q,
+                             ldq, scales, rows, cols / BQ);
+    if (in_dtype == B200_DT_F16)
+        return launch_kernel(quant_blocks128_kernel<__half, PER_ROW>, grid, dim3(512), 0, stream, (const __half *)x, ldx,
+                             q, ldq, scales, rows, cols / BQ);
+    return launch_kernel(quant_blocks128_kernel<__nv_bfloat16, PER_ROW>, grid, dim3(512), 0, stream,
+                         (const __nv_bfloat16 *)x, ldx, q, ldq, scales, rows, cols / BQ);
+}
+
 int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
-                       int cols, cudaStream_t stream) {
+                       int cols, int per_row, cudaStream_t stream) {
     if (!x || !q || !scales || rows <= 0 || cols <= 0) return fail("invalid quantize_blocks128 arguments");
     if (cols % BQ != 0) return fail("quantize_blocks128 needs a column count divisible by 128, got %d", cols);
     const size_t esz = in_dtype == B200_DT_F32 ? 4 : 2;
@@ -542,18 +571,9 @@ int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, lo
         return fail("quantize_blocks128 reads fp32, fp16 or bf16");
     if (ldx < cols || ldq < cols || !aligned16(x) || !aligned16(q) || ((size_t)ldx * esz) % 16 != 0 || ldq % 16 != 0)
         return fail("quantize_blocks128 needs 16-byte aligned buffers and row strides (ldx=%lld, ldq=%lld)", ldx, ldq);
-    const dim3 grid((unsigned)(cols / BQ), (unsigned)((rows + BQ - 1) / BQ));
-    if (grid.y > 65535u) return fail("quantize_blocks128: more than 65535 block rows");
-    cudaError_t e;
-    if (in_dtype == B200_DT_F32)
-        e = launch_kernel(quant_blocks128_kernel<float>, grid, dim3(512), 0, stream, (const float *)x, ldx, q, ldq, scales,
-                          rows, cols / BQ);
-    else if (in_dtype == B200_DT_F16)
-        e = launch_kernel(quant_blocks128_kernel<__half>, grid, dim3(512), 0, stream, (const __half *)x, ldx, q, ldq,
-                          scales, rows, cols / BQ);
-    else
-        e = launch_kernel(quant_blocks128_kernel<__nv_bfloat16>, grid, dim3(512), 0, stream, (const __nv_bfloat16 *)x,
-                          ldx, q, ldq, scales, rows, cols / BQ);
+    if ((rows + BQ - 1) / BQ > 65535) return fail("quantize_blocks128: more than 65535 block rows");
+    const cudaError_t e = per_row ? launch_quant_blocks<true>(x, in_dtype, ldx, q, ldq, scales, rows, cols, stream)
+                                  : launch_quant_blocks<false>(x, in_dtype, ldx, q, ldq, scales, rows, cols, stream);
     if (e != cudaSuccess) return fail("launching quant_blocks128: %s", cudaGetErrorString(e));
     return check_launch("quant_blocks128");
 }

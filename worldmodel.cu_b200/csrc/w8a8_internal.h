@@ -158,7 +158,8 @@ void gemm_reset_static_tickets();
 // scale = max(amax, 1e-8) / 128, codes in [-128, 127], fp32 accumulation K block by K block)
 struct Blocks128Args {
     const int8_t *x;         // codes [m, k], row stride k
-    const float *x_scales;   // [ceil(m / 128)][k / 128]
+    const float *x_scales;   // [ceil(m / 128)][k / 128], or [m][k / 128] with x_scale_per_row
+    int x_scale_per_row;     // activations quantized in 1 x 128 groups (a scale per row and K block)
     const int8_t *w;         // codes, row-major [n, k] or slab layout
     int w_layout;
     const float *w_scales;   // [ceil(n / 128)][k / 128]
@@ -173,7 +174,7 @@ struct Blocks128Args {
     int m, k, n;
 };
 int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
-                       int cols, cudaStream_t stream);
+                       int cols, int per_row, cudaStream_t stream);
 int linear_blocks128(const Blocks128Args &a, cudaStream_t stream);
 
 // ---- status.cu
