@@ -784,11 +784,16 @@ def run_blockwise(pkg, stream, rows=8192, n_weights=8):
         sw_blk = torch.rand((n + 127) // 128, k // 128, device=dev) * 1e-4 + 1e-5
         sw_row = torch.rand(n, device=dev) * 1e-4 + 1e-5
         qb, sb = pkg.quantize_blocks128(x)
+        qg, sg = pkg.quantize_blocks128(x, block_rows=1)
         qr, sr = pkg.quantize_rows(x)
 
         def lin_blocks():
             for w in wq:
                 pkg.linear_blocks128(qb, sb, w, sw_blk, n=n, out=y)
+
+        def lin_groups():  # 1 x 128 activation groups: a scale per token row and K block
+            for w in wq:
+                pkg.linear_blocks128(qg, sg, w, sw_blk, n=n, out=y, x_block_rows=1)
 
         def lin_rows():
             for w in wq:
@@ -805,7 +810,8 @@ def run_blockwise(pkg, stream, rows=8192, n_weights=8):
                                                   torch.cuda.current_stream().cuda_stream)
 
         res = {}
-        for key, run in (("blockwise_linear_us", lin_blocks), ("row_channel_linear_us", lin_rows),
+        for key, run in (("blockwise_linear_us", lin_blocks), ("row_group_linear_us", lin_groups),
+                         ("row_channel_linear_us", lin_rows),
                          ("block_quantizer_us", quant_blocks), ("row_quantizer_us", quant_rows)):
             with torch.cuda.stream(stream):
                 run()
