@@ -827,6 +827,35 @@ def run_blockwise(pkg, stream, rows=8192, n_weights=8):
         res["blockwise_tops"] = ops / res["blockwise_linear_us"] * 1e-6
         res["row_channel_tops"] = ops / res["row_channel_linear_us"] * 1e-6
         out[f"{name}_{k}x{n}"] = res
+    # fp16 activation quantizer + linear at M=128 on the reference model's four shapes: the quantity the reference's
+    # notes time for a third-party blockwise kernel on other hardware (docs/cuda_w8a8_optimization.md:344-347)
+    small = {}
+    for name, k, n in (("qkv", D_MODEL, 4096), ("out", D_MODEL, D_MODEL), ("fc1", D_MODEL, D_HIDDEN), ("fc2", D_HIDDEN, D_MODEL)):
+        x = torch.randn(128, k, device=dev, dtype=torch.float16)
+        y = torch.empty(128, n, device=dev, dtype=torch.float16)
+        wq = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device=dev) for _ in range(n_weights)]
+        sw_blk = torch.rand((n + 127) // 128, k // 128, device=dev) * 1e-4 + 1e-5
+        qb = torch.empty(128, k, dtype=torch.int8, device=dev)
+        sb = torch.empty(1, k // 128, device=dev)
+
+        def quant_then_linear():
+            st = torch.cuda.current_stream().cuda_stream
+            for w in wq:
+                pkg.lib().b200_w8a8_quantize_blocks128(x.data_ptr(), pkg.DT_F16, k, qb.data_ptr(), k, sb.data_ptr(), 128, k,
+                                                       128, st)
+                pkg.linear_blocks128(qb, sb, w, sw_blk, n=n, out=y)
+
+        with torch.cuda.stream(stream):
+            quant_then_linear()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            quant_then_linear()
+        with torch.cuda.stream(stream):
+            graph.replay()
+        ms, _, _ = time_steps(graph.replay, 5, stream, lambda: None)
+        small[f"{name}_{k}x{n}_us"] = ms / (5 * n_weights) * 1e3
+    out["m128_quant_plus_linear"] = small
     return out
 
 
