@@ -307,6 +307,11 @@ int b200_w8a8_pack_weight_host(const float *w_host, int n, int k, int layout, in
  * K must be a multiple of 128; code and y buffers 16-byte aligned with 16-byte aligned rows. */
 int b200_w8a8_quantize_blocks128(const void *x, int x_dtype, int64_t ldx, int8_t *q, int64_t ldq, float *block_scales,
                                  int rows, int cols, int block_rows, void *stream);
+/* The Norm -> A8 fusion (b200_w8a8_rms_norm_quantize_rows) with 1 x 128 groups: (Ada)RMSNorm of each row in fp32
+ * (fp64 sum of squares), then one scale per row and K block; group_scales [rows][cols / 128]; cols <= 8192. */
+int b200_w8a8_rms_norm_quantize_row_blocks128(const void *x, int x_dtype, int64_t ldx, const float *vec_scale,
+                                              int scale_is_mod, const float *vec_bias, int8_t *q, int64_t ldq,
+                                              float *group_scales, int rows, int cols, float eps, void *stream);
 int b200_w8a8_pack_weight_blocks128_host(const float *w_host, int n, int k, int layout, int8_t *packed_host,
                                          float *block_scales_host, int threads);
 int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, const int8_t *w_i8, int w_layout,

@@ -365,6 +365,11 @@ def quantize_row_blocks128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]
     return q.view(rows, cols).contiguous(), scale
 
 
+def rms_norm_quantize_row_blocks128(x, mod_scale=None, bias=None, eps=1e-6, scale_is_mod=True):
+    """Fused (Ada)RMSNorm (`rms_norm_rows`) -> 1 x 128 group codes."""
+    return quantize_row_blocks128(rms_norm_rows(x, mod_scale, bias, eps, scale_is_mod))
+
+
 def fma_f32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
     """Correctly rounded fp32 fused multiply-add a * b + c for fp32 inputs whose product is exact in fp64 (here a is
     an integer of at most 22 bits).  The product is formed exactly in fp64; adding c rounds once to fp64 and the

@@ -275,6 +275,42 @@ def test_row_groups_keep_ordinary_rows_next_to_outlier_rows(pkg, ref):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols,form", [(1, 128, "gamma"), (77, 384, "mod_bias"), (300, 2048, "gamma"),
+                                            (64, 4096, "none"), (33, 8192, "mod_bias")])
+def test_fused_rms_norm_row_group_quantizer_bit_exact(pkg, ref, rows, cols, form, dtype):
+    g = torch.Generator().manual_seed(rows + cols)
+    x = acts(rows, cols, rows * 3 + cols, dtype)
+    vec = None if form == "none" else torch.randn(cols, generator=g) * 0.2 + (0.0 if form == "mod_bias" else 1.0)
+    bias = torch.randn(cols, generator=g) * 0.1 if form == "mod_bias" else None
+    is_mod = form == "mod_bias"
+    dv = lambda t: None if t is None else t.to(DEV)
+    q, s = pkg.rms_norm_quantize_row_blocks128(x.to(DEV), dv(vec), dv(bias), eps=1e-6, scale_is_mod=is_mod)
+    q_ref, s_ref = ref.rms_norm_quantize_row_blocks128(x, vec, bias, 1e-6, is_mod)
+    assert torch.equal(s.cpu().view(torch.int32), s_ref.view(torch.int32))
+    assert torch.equal(q.cpu(), q_ref)
+
+
+@pytest.mark.gpu
+def test_norm_then_blockwise_linear_chain_matches_the_oracle(pkg, ref):
+    """RMSNorm -> group codes -> blockwise linear + residual, the three operators of an attention-out style step."""
+    g = torch.Generator().manual_seed(41)
+    m, d, n = 200, 1024, 1024
+    x = (torch.randn(m, d, generator=g) * 1.5).to(torch.float16)
+    gamma = torch.randn(d, generator=g) * 0.05 + 1.0
+    w = torch.randn(n, d, generator=g) * 0.03
+    q, s = pkg.rms_norm_quantize_row_blocks128(x.to(DEV), gamma.to(DEV), None, eps=1e-6, scale_is_mod=False)
+    packed, sw = pkg.pack_weight_blocks128(w)
+    y = pkg.linear_blocks128(q, s, packed.to(DEV), sw.to(DEV), n=n, residual=x.to(DEV), out_dtype=torch.float16,
+                             x_block_rows=1)
+    torch.cuda.synchronize()
+    q_ref, s_ref = ref.rms_norm_quantize_row_blocks128(x, gamma, None, 1e-6, False)
+    qw_ref, sw_ref = ref.quantize_blocks128(w)
+    want = ref.linear_blocks128(q_ref, s_ref, qw_ref, sw_ref, residual=x, out_dtype=torch.float16, x_scale_per_row=True)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(y.cpu(), want)
+
+
+@pytest.mark.gpu
 def test_accuracy_on_config0_outlier_channels(pkg, ref, parity_log):
     """Config 0 (fp16 tokens with eight x20 outlier channels, N(0, 0.02) weights): SQNR against the fp64 product of the
     row/channel rule, of 128 x 128 blocks on both operands, and of 1 x 128 activation groups with 128 x 128 weight

@@ -75,6 +75,8 @@ _PROTOTYPES = {
     "b200_w8a8_pack_weight_blocks128_host": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int]),
     "b200_w8a8_quantize_blocks128": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int,
                                              c_void_p]),
+    "b200_w8a8_rms_norm_quantize_row_blocks128": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                                                          c_int64, c_void_p, c_int, c_int, c_float, c_void_p]),
     "b200_w8a8_linear_blocks128": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_int64, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_w8a8_stack_create": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]),
@@ -380,6 +382,18 @@ def quantize_blocks128(x, block_rows=128):
                     device=x.device)
     _check(lib().b200_w8a8_quantize_blocks128(_ptr(x), _dt(x), x.stride(0), _ptr(q), cols, _ptr(s), rows, cols,
                                               block_rows, _stream()), "quantize_blocks128")
+    return q, s
+
+
+def rms_norm_quantize_row_blocks128(x, vec_scale=None, bias=None, eps=1e-6, scale_is_mod=True):
+    """Fused (Ada)RMSNorm -> codes with one scale per row and 128-wide K block.  Returns (int8 [rows, cols], fp32 [rows, cols/128])."""
+    import torch
+    rows, cols = x.shape
+    q = torch.empty(rows, cols, dtype=torch.int8, device=x.device)
+    s = torch.empty(rows, max(cols // 128, 1), dtype=torch.float32, device=x.device)
+    _check(lib().b200_w8a8_rms_norm_quantize_row_blocks128(_ptr(x), _dt(x), x.stride(0), _ptr(vec_scale), int(scale_is_mod),
+                                                           _ptr(bias), _ptr(q), cols, _ptr(s), rows, cols, eps, _stream()),
+           "rms_norm_quantize_row_blocks128")
     return q, s
 
 

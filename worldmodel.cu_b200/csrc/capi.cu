@@ -249,6 +249,14 @@ int b200_w8a8_quantize_blocks128(const void *x, int x_dtype, int64_t ldx, int8_t
     return quantize_blocks128(x, x_dtype, ldx, q, ldq, block_scales, rows, cols, block_rows == 1, as_stream(stream));
 }
 
+int b200_w8a8_rms_norm_quantize_row_blocks128(const void *x, int x_dtype, int64_t ldx, const float *vec_scale,
+                                              int scale_is_mod, const float *vec_bias, int8_t *q, int64_t ldq,
+                                              float *group_scales, int rows, int cols, float eps, void *stream) {
+    if (status_check_entry()) return 1;
+    return rms_norm_quantize_row_blocks128(x, x_dtype, ldx, vec_scale, scale_is_mod, vec_bias, q, ldq, group_scales, rows,
+                                           cols, eps, as_stream(stream));
+}
+
 int b200_w8a8_linear_blocks128(const int8_t *x_i8, const float *x_block_scales, const int8_t *w_i8, int w_layout,
                                const float *w_block_scales, const float *bias, const float *gate, const void *residual,
                                int64_t ldr, void *y, int y_dtype, int64_t ldy, int m, int k, int n, int act,

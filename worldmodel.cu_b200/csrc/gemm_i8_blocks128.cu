@@ -465,6 +465,136 @@ __global__ void __launch_bounds__(512, 2) quant_blocks128_kernel(const T *__rest
     }
 }
 
+// ---------------------------------------------------------------- fused (Ada)RMSNorm -> 1 x 128 group codes
+// The Norm -> A8 fusion of the row/channel path (src/world_cuda_ops.cu:129-182 is what that one replaces) with
+// the blockwise rule on 1 x 128 groups: one CTA per row, thread t owns the 8-element vectors t, t + 256, ...
+// of the row (read once, kept in registers), the sum of squares is accumulated in fp64 and reduced over the CTA,
+// the 16 threads that own one 128-column group share its maximum with four shuffles.
+template <typename T>
+__device__ __forceinline__ void load8(const T *p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float *p, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half *p, float (&v)[8]) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+        v[2 * k] = f.x;
+        v[2 * k + 1] = f.y;
+    }
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16 *p, float (&v)[8]) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        v[2 * k] = __uint_as_float(w[k] << 16);
+        v[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+    }
+}
+
+struct RmsGroupArgs {
+    const void *x;
+    long long ldx;
+    const float *vec_scale;  // gamma or modulation [cols], nullable
+    int scale_is_mod;        // 1: multiply by (1 + vec_scale)
+    const float *vec_bias;   // [cols], nullable
+    int8_t *q;
+    long long ldq;
+    float *scales;           // [rows][cols / 128]
+    int rows, cols;
+    float eps;
+    double inv_cols;         // 1 / cols when that is exact (cols a power of two), else 0: divide
+};
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) rms_quant_row_groups_kernel(const RmsGroupArgs a) {
+    __shared__ double red[8];
+    pdl_trigger();
+    const int row = blockIdx.x, t = threadIdx.x;
+    const int nvec = a.cols >> 3;
+    const T *xrow = reinterpret_cast<const T *>(a.x) + (long long)row * a.ldx;
+    float v[NV][8];
+    pdl_wait();
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int vi = t + 256 * j;
+        if (vi < nvec) {
+            load8<T>(xrow + 8 * vi, v[j]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[j][i] = 0.0f;
+        }
+    }
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const double d = (double)v[j][i];
+            ss = fma(d, d, ss);
+        }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((t & 31) == 0) red[t >> 5] = ss;
+    __syncthreads();
+    double tot = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) tot += red[i];
+    const double mean = a.inv_cols != 0.0 ? tot * a.inv_cols : tot / (double)a.cols;
+    const float inv_rms = (float)rsqrt(mean + (double)a.eps);
+    const int k_blocks = a.cols >> 7;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int vi = t + 256 * j;
+        const bool has = vi < nvec;  // uniform over the 16 threads of a group: groups are whole
+        float amax = 0.0f;
+        if (has) {
+            const int col = 8 * vi;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float u = __fmul_rn(v[j][i], inv_rms);
+                if (a.vec_scale) {
+                    const float s = __ldg(a.vec_scale + col + i);
+                    u = __fmul_rn(u, a.scale_is_mod ? __fadd_rn(1.0f, s) : s);
+                }
+                if (a.vec_bias) u = __fadd_rn(u, __ldg(a.vec_bias + col + i));
+                v[j][i] = u;
+                amax = fmaxf(amax, fabsf(u));
+            }
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (!has) continue;
+        BlockScale bs;
+        bs.scale = __fmul_rn(fmaxf(amax, 1e-8f), 0.0078125f);
+        bs.inv = bs.scale < 1e30f ? __frcp_rn(bs.scale) : 0.0f;
+        if ((t & 15) == 0) a.scales[(long long)row * k_blocks + (vi >> 4)] = bs.scale;
+        uint32_t w[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            w[h] = (uint32_t)(block_code(v[j][4 * h], bs) & 0xFF) | ((uint32_t)(block_code(v[j][4 * h + 1], bs) & 0xFF) << 8) |
+                   ((uint32_t)(block_code(v[j][4 * h + 2], bs) & 0xFF) << 16) |
+                   ((uint32_t)(block_code(v[j][4 * h + 3], bs) & 0xFF) << 24);
+        *reinterpret_cast<uint2 *>(a.q + (long long)row * a.ldq + 8 * vi) = make_uint2(w[0], w[1]);
+    }
+}
+
+template <typename T>
+static cudaError_t launch_rms_groups(const RmsGroupArgs &a, cudaStream_t stream) {
+    const int nvec = a.cols / 8;
+    const dim3 grid((unsigned)a.rows);
+    if (nvec <= 256) return launch_kernel(rms_quant_row_groups_kernel<T, 1>, grid, dim3(256), 0, stream, a);
+    if (nvec <= 512) return launch_kernel(rms_quant_row_groups_kernel<T, 2>, grid, dim3(256), 0, stream, a);
+    return launch_kernel(rms_quant_row_groups_kernel<T, 4>, grid, dim3(256), 0, stream, a);
+}
+
 struct BlocksDeviceInfo {
     bool attr_set[3][2] = {};
 };
@@ -576,6 +706,30 @@ int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, lo
                                   : launch_quant_blocks<false>(x, in_dtype, ldx, q, ldq, scales, rows, cols, stream);
     if (e != cudaSuccess) return fail("launching quant_blocks128: %s", cudaGetErrorString(e));
     return check_launch("quant_blocks128");
+}
+
+int rms_norm_quantize_row_blocks128(const void *x, int in_dtype, long long ldx, const float *vec_scale, int scale_is_mod,
+                                    const float *vec_bias, int8_t *q, long long ldq, float *scales, int rows, int cols,
+                                    float eps, cudaStream_t stream) {
+    if (!x || !q || !scales || rows <= 0 || cols <= 0) return fail("invalid rms_norm_quantize_row_blocks128 arguments");
+    if (cols % BQ != 0 || cols > 8192)
+        return fail("rms_norm_quantize_row_blocks128 needs a column count divisible by 128, at most 8192; got %d", cols);
+    if (in_dtype != B200_DT_F32 && in_dtype != B200_DT_F16 && in_dtype != B200_DT_BF16)
+        return fail("rms_norm_quantize_row_blocks128 reads fp32, fp16 or bf16");
+    const size_t esz = in_dtype == B200_DT_F32 ? 4 : 2;
+    if (ldx < cols || ldq < cols || !aligned16(x) || ((size_t)ldx * esz) % 16 != 0 ||
+        (reinterpret_cast<uintptr_t>(q) & 7u) != 0 || ldq % 8 != 0)
+        return fail("rms_norm_quantize_row_blocks128 needs 16-byte aligned input rows and 8-byte aligned code rows");
+    RmsGroupArgs a{};
+    a.x = x; a.ldx = ldx; a.vec_scale = vec_scale; a.scale_is_mod = scale_is_mod; a.vec_bias = vec_bias;
+    a.q = q; a.ldq = ldq; a.scales = scales; a.rows = rows; a.cols = cols; a.eps = eps;
+    a.inv_cols = (cols & (cols - 1)) == 0 ? 1.0 / (double)cols : 0.0;
+    cudaError_t e;
+    if (in_dtype == B200_DT_F32) e = launch_rms_groups<float>(a, stream);
+    else if (in_dtype == B200_DT_F16) e = launch_rms_groups<__half>(a, stream);
+    else e = launch_rms_groups<__nv_bfloat16>(a, stream);
+    if (e != cudaSuccess) return fail("launching rms_quant_row_groups: %s", cudaGetErrorString(e));
+    return check_launch("rms_quant_row_groups");
 }
 
 int linear_blocks128(const Blocks128Args &a, cudaStream_t stream) {

@@ -176,6 +176,9 @@ struct Blocks128Args {
 int quantize_blocks128(const void *x, int in_dtype, long long ldx, int8_t *q, long long ldq, float *scales, int rows,
                        int cols, int per_row, cudaStream_t stream);
 int linear_blocks128(const Blocks128Args &a, cudaStream_t stream);
+int rms_norm_quantize_row_blocks128(const void *x, int in_dtype, long long ldx, const float *vec_scale, int scale_is_mod,
+                                    const float *vec_bias, int8_t *q, long long ldq, float *scales, int rows, int cols,
+                                    float eps, cudaStream_t stream);
 
 // ---- status.cu
 // Device-visible address of the status word (pinned host memory mapped into the device when
