@@ -369,3 +369,59 @@ def test_blockwise_linear_rejects_bad_arguments(pkg):
     out = torch.empty(16, 104, dtype=torch.float16, device=DEV)[:, 1:101]
     with pytest.raises(pkg.W8A8Error, match="aligned"):
         pkg.linear_blocks128(qx, s, w, s, n=100, w_layout=pkg.W_ROW_MAJOR, out=out)
+
+
+@pytest.mark.gpu
+def test_four_layers_row_group_numerics_against_the_row_channel_stack(pkg, ref, parity_log):
+    """The ten-operator layer of the linear stack (norm -> A8 -> QKV -> A8 -> out + residual -> norm -> A8 -> controller +
+    residual -> norm -> A8 -> up + GELU -> A8 -> down + residual) composed from the blockwise operators with a scale per
+    token row and K block, next to the row/channel stack driver, both against the same layers in fp64 without any
+    quantization: synthetic tokens with eight x20 outlier channels, four layers."""
+    d, nqkv, hid, rows, n_layers = 512, 1536, 2048, 256, 4
+    layers = [ref.make_layer_fp32(l, d, nqkv, hid) for l in range(n_layers)]
+    x = ref.make_tokens(rows, 3, torch.float16, d)
+
+    def rms(v, g):
+        return v / torch.sqrt((v * v).mean(dim=1, keepdim=True) + 1e-6) * g.double()
+
+    ideal = x.double()
+    for ws, gs in layers:
+        w = [t.double() for t in ws]
+        ideal = ideal + (rms(ideal, gs[0]) @ w[0].T)[:, :d] @ w[1].T
+        ideal = ideal + rms(ideal, gs[1]) @ w[2].T
+        ideal = ideal + torch.nn.functional.gelu(rms(ideal, gs[2]) @ w[3].T, approximate="tanh") @ w[4].T
+
+    stack = pkg.LinearStack(d, nqkv, hid, n_layers, max_rows=rows)
+    for l, (ws, gs) in enumerate(layers):
+        stack.set_layer(l, ws, gs)
+    y_rows = stack.forward(x.to(DEV)).cpu()
+    stack.close()
+
+    cur = x.to(DEV)
+    for ws, gs in layers:
+        packed = [tuple(t.to(DEV) for t in pkg.pack_weight_blocks128(w)) for w in ws]
+        g = [t.to(DEV) for t in gs]
+        lin = lambda q, s, i, n, **kw: pkg.linear_blocks128(q, s, packed[i][0], packed[i][1], n=n, x_block_rows=1, **kw)
+        q, s = pkg.rms_norm_quantize_row_blocks128(cur, g[0], None, scale_is_mod=False)
+        qkv = lin(q, s, 0, nqkv, out_dtype=torch.float16)
+        q, s = pkg.quantize_blocks128(qkv[:, :d], block_rows=1)
+        x1 = lin(q, s, 1, d, residual=cur, out_dtype=torch.float16)
+        q, s = pkg.rms_norm_quantize_row_blocks128(x1, g[1], None, scale_is_mod=False)
+        x2 = lin(q, s, 2, d, residual=x1, out_dtype=torch.float16)
+        q, s = pkg.rms_norm_quantize_row_blocks128(x2, g[2], None, scale_is_mod=False)
+        h = lin(q, s, 3, hid, act=pkg.ACT_GELU_TANH, out_dtype=torch.float32)
+        q, s = pkg.quantize_blocks128(h, block_rows=1)
+        cur = lin(q, s, 4, d, residual=x2, out_dtype=torch.float16)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    y_groups = cur.cpu()
+    db_rows = ref.sqnr_db(ideal.float(), y_rows.float())
+    db_groups = ref.sqnr_db(ideal.float(), y_groups.float())
+    # the same for what the four layers added to the stream (the stream itself is carried exactly in both)
+    delta = (ideal - x.double()).float()
+    dd_rows = ref.sqnr_db(delta, y_rows.float() - x.float())
+    dd_groups = ref.sqnr_db(delta, y_groups.float() - x.float())
+    parity_log("four_layer_stack_sqnr_db", 0, ideal.numel(), row_channel=db_rows, groups_1x128=db_groups,
+               update_row_channel=dd_rows, update_groups_1x128=dd_groups)
+    assert db_groups > db_rows + 1.0, (db_rows, db_groups)
+    assert dd_groups > dd_rows + 1.0, (dd_rows, dd_groups)
