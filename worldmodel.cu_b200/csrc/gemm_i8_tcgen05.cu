@@ -622,6 +622,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t cta_rank = cluster_cta_rank();  // 0 = leader
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    // K slabs per stage: with 2, one copy per operand brings a box two slabs deep (half the copies for the same
+    // bytes in flight: three stages of 64 KB instead of six of 32 KB); a stage then feeds eight MMAs.
+    const int kd = p.slabs_per_stage;
+    const int n_stages = kPairStages / kd;
+    const int stage_bytes = kd * kPairStageBytes;
+    const int b_off = kd * BM * BK;  // the W slabs of a stage follow its A slabs
 
     pdl_trigger();
     if (threadIdx.x == 0) {
@@ -651,24 +657,44 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     if (warp == 0) {
         if (lane == 0) {
-            pdl_wait();
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            // Weights that nothing in the stream writes: the W tiles of the first ring are requested before the
+            // predecessor kernel (whose output is the A operand) has finished; the A tiles follow after the wait.
+            int prefetched = 0;
+            if (p.static_weights && pair_id < p.num_tiles) {
+                int m_blk, n_blk;
+                decode_tile(p, pair_id, m_blk, n_blk);
+                const int n0 = n_blk * BN + (int)cta_rank * (BN / 2);
+                prefetched = min(p.num_k_blocks / kd, n_stages);
+                for (int i = 0; i < prefetched; ++i) {
+                    const uint32_t full_in_leader = cluster_map_shared(smem_u32(&bar_full[i]), 0);
+                    if (cta_rank == 0) mbar_arrive_expect_tx(&bar_full[i], 2u * (uint32_t)stage_bytes);
+                    tma_load_3d_pair(smem + i * stage_bytes + b_off, &tm_b, full_in_leader, (i * kd) * p.b_kx, n0,
+                                     (i * kd) * p.b_kz);
+                }
+            }
+            pdl_wait();
             for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
                 int m_blk, n_blk;
                 decode_tile(p, tile, m_blk, n_blk);
                 const int m0 = m_blk * 2 * BM + (int)cta_rank * BM;
                 const int n0 = n_blk * BN + (int)cta_rank * (BN / 2);
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
-                    ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
-                    if (!ok) break;
-                    uint8_t *sa = smem + s * kPairStageBytes;
+                for (int kb = 0; kb < p.num_k_blocks; kb += kd) {
+                    uint8_t *sa = smem + s * stage_bytes;
                     const uint32_t full_in_leader = cluster_map_shared(smem_u32(&bar_full[s]), 0);
-                    if (cta_rank == 0) mbar_arrive_expect_tx(&bar_full[s], 2u * kPairStageBytes);  // both CTAs' bytes
-                    tma_load_3d_pair(sa, &tm_a, full_in_leader, kb * BK, m0, 0);
-                    tma_load_3d_pair(sa + BM * BK, &tm_b, full_in_leader, kb * p.b_kx, n0, kb * p.b_kz);
-                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                    if (prefetched > 0) {
+                        --prefetched;  // stage already armed, its W tile already requested
+                        tma_load_3d_pair(sa, &tm_a, full_in_leader, kb * p.a_kx, m0, kb * p.a_kz);
+                    } else {
+                        ok = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, wctx, KS_TIMEOUT_SMEM_EMPTY);
+                        if (!ok) break;
+                        if (cta_rank == 0) mbar_arrive_expect_tx(&bar_full[s], 2u * (uint32_t)stage_bytes);  // both CTAs' bytes
+                        tma_load_3d_pair(sa, &tm_a, full_in_leader, kb * p.a_kx, m0, kb * p.a_kz);
+                        tma_load_3d_pair(sa + b_off, &tm_b, full_in_leader, kb * p.b_kx, n0, kb * p.b_kz);
+                    }
+                    if (++s == n_stages) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -687,20 +713,22 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * BN);
-                for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (int kb = 0; kb < p.num_k_blocks; kb += kd) {
                     ok = mbar_wait_bounded(&bar_full[s], ph, wctx, KS_TIMEOUT_SMEM_FULL);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_u32(smem + s * kPairStageBytes);
-                    const uint64_t da = umma_smem_desc_k128(sa);
-                    const uint64_t db = umma_smem_desc_k128(sa + BM * BK);
+                    const uint32_t sa = smem_u32(smem + s * stage_bytes);
+                    for (int d = 0; d < kd; ++d) {
+                        const uint64_t da = umma_smem_desc_k128(sa + (uint32_t)(d * BM * BK));
+                        const uint64_t db = umma_smem_desc_k128(sa + (uint32_t)(b_off + d * BM * BK));
 #pragma unroll
-                    for (int j = 0; j < BK / 32; ++j)
-                        umma_i8_pair(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc,
-                                     (uint32_t)((kb | j) != 0));
+                        for (int j = 0; j < BK / 32; ++j)
+                            umma_i8_pair(d_tmem, da + (uint64_t)(2 * j), db + (uint64_t)(2 * j), idesc,
+                                         (uint32_t)((kb | d | j) != 0));
+                    }
                     umma_commit_pair(smem_u32(&bar_empty[s]));                         // my own stage is free
                     umma_commit_pair(cluster_map_shared(smem_u32(&bar_empty[s]), 1));  // and the peer's
-                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                    if (++s == n_stages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) {
                     umma_commit_pair(smem_u32(&bar_tfull[b]));
@@ -1097,10 +1125,27 @@ int launch_pair(const LinearArgs &a, GemmParams &p, cudaStream_t stream) {
     p.kb_per_split = p.num_k_blocks;
     p.num_work = p.num_tiles;
     p.a_stage_bytes = BM * BK;
+    // two K slabs per stage (operands described slab by slab, one copy takes a box two slabs deep) whenever the
+    // slab count is even
+    const bool two_slabs = a.k % (2 * BK) == 0 && !g_one_slab_stages;
+    p.slabs_per_stage = two_slabs ? 2 : 1;
     CUtensorMap tm_a, tm_b, tm_out;
-    if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m, BM)) return 1;
+    if (two_slabs) {
+        if (make_map(&tm_a, a.x, BK, (uint64_t)a.m, (uint64_t)(a.k / BK), (uint64_t)a.k, BK, BM, 2)) return 1;
+        p.a_kx = 0;
+        p.a_kz = 1;
+    } else {
+        if (make_map(&tm_a, a.x, (uint64_t)a.k, (uint64_t)a.m, 1, (uint64_t)a.k, (uint64_t)a.k * (uint64_t)a.m, BM)) return 1;
+        p.a_kx = BK;
+        p.a_kz = 0;
+    }
     if (a.w_layout == B200_W_SLAB128) {
-        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, 128)) return 1;
+        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), BK, (uint64_t)a.n * BK, 128, two_slabs ? 2 : 1))
+            return 1;
+        p.b_kx = 0;
+        p.b_kz = 1;
+    } else if (two_slabs) {
+        if (make_map(&tm_b, a.w, BK, (uint64_t)a.n, (uint64_t)(a.k / BK), (uint64_t)a.k, BK, 128, 2)) return 1;
         p.b_kx = 0;
         p.b_kz = 1;
     } else {
@@ -1307,13 +1352,22 @@ int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_byte
     }
     p.splits = pl.splits;
     p.split_mode = pl.mode;
-    // CTA pairs: lean epilogue, unsplit 256-wide tiles, at least two row blocks.  Worth it once the
-    // grid is full enough for the operand feed to be the limit.
-    const bool pair_legal = pl.bn == 256 && pl.splits == 1 && a.m > BM && p.tma_store && p.vec_ok && (a.n % 32 == 0);
+    // CTA pairs: lean epilogue, unsplit 256 x 256 tiles, at least two row blocks.  With two K slabs per stage
+    // (K a multiple of 256) the pair kernel measured 4 - 14 % faster than the planner's single-CTA choice from
+    // 96 pair tiles of 16 K slabs upwards, and from 64 pair tiles when K is 8192 (M=2048: 29.8 -> 26.9 us); below
+    // that (48 - 64 pair tiles of 16 slabs) it is 4 % slower.  With one slab per stage it only pays once the grid
+    // runs many waves.
+    const bool no_forced_plan = force_bn == 0 && force_splits == 0;
+    const bool pair_legal = (pl.bn == 256 || no_forced_plan) && (pl.splits == 1 || no_forced_plan) && a.m > BM &&
+                            p.tma_store && p.vec_ok && (a.n % 32 == 0);
     const long long pair_tiles = (long long)((a.m + 255) / 256) * ((a.n + 255) / 256);
-    // measured on B200: +3 % at M=16384 (many waves of tiles), neutral to negative below ~4 waves
-    const bool pair_wanted = g_pair_mode == 1 || (g_pair_mode == 0 && pair_tiles >= 2 * device_sms());
+    const long long pair_slabs = pair_tiles * ((a.k + BK - 1) / BK);
+    const bool pair_two_slabs = a.k % (2 * BK) == 0 && !g_one_slab_stages;
+    const bool pair_pays = pair_two_slabs ? (pair_tiles >= 64 && pair_slabs >= 96 * 16) : pair_tiles >= 2 * device_sms();
+    const bool pair_wanted = g_pair_mode == 1 || (g_pair_mode == 0 && pair_pays);
     if (pair_legal && pair_wanted && g_pair_mode != 2) {
+        p.splits = 1;
+        p.split_mode = 0;
         switch (a.out_dtype) {
             case B200_DT_S32: return launch_pair<B200_DT_S32>(a, p, stream);
             case B200_DT_F32: return launch_pair<B200_DT_F32>(a, p, stream);
