@@ -37,7 +37,7 @@ LINEARS = [("qkv", N_QKV, D_MODEL), ("out", D_MODEL, D_MODEL), ("ctrl", D_MODEL,
 OPS_PER_ROW_LAYER = 2 * sum(n * k for _, n, k in LINEARS)  # 109,051,904
 WEIGHT_BYTES_LAYER = sum(n * k for _, n, k in LINEARS)     # 54,525,952
 # DRAM read+write of the five GEMM launches of one layer from the committed ncu captures (profiles/)
-NCU_DRAM_BYTES_PER_LAYER = {512: 69.6e6, 2048: 129.7e6, 8192: 675.2e6}
+NCU_DRAM_BYTES_PER_LAYER = {512: 69.6e6, 2048: 129.7e6, 8192: 668.5e6}
 WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),

@@ -1353,17 +1353,19 @@ int gemm_launch_impl(const LinearArgs &a, void *workspace, size_t workspace_byte
     p.splits = pl.splits;
     p.split_mode = pl.mode;
     // CTA pairs: lean epilogue, unsplit 256 x 256 tiles, at least two row blocks.  With two K slabs per stage
-    // (K a multiple of 256) the pair kernel measured 4 - 14 % faster than the planner's single-CTA choice from
-    // 96 pair tiles of 16 K slabs upwards, and from 64 pair tiles when K is 8192 (M=2048: 29.8 -> 26.9 us); below
-    // that (48 - 64 pair tiles of 16 slabs) it is 4 % slower.  With one slab per stage it only pays once the grid
-    // runs many waves.
+    // (K a multiple of 256) the pair kernel measured 7 - 12 % faster than the single-CTA kernel on the wide and
+    // the deep linears of an 8192-row band, weights streamed from HBM (QKV 81.8 -> 78.1 us, down 116.4 -> 102.3).
+    // With warm weights it already wins from 96 pair tiles of 16 slabs, but with cold weights and few tiles per
+    // pair its longer fill (64 KB per CTA before the first MMA, a cluster launch) eats that: M=2048 is neutral in
+    // the chained stack and the 2048 x 2048 linears of a band are 3 % behind.  Hence the threshold in pair tiles
+    // x K slabs.  With one slab per stage it only pays once the grid runs many waves.
     const bool no_forced_plan = force_bn == 0 && force_splits == 0;
     const bool pair_legal = (pl.bn == 256 || no_forced_plan) && (pl.splits == 1 || no_forced_plan) && a.m > BM &&
                             p.tma_store && p.vec_ok && (a.n % 32 == 0);
     const long long pair_tiles = (long long)((a.m + 255) / 256) * ((a.n + 255) / 256);
     const long long pair_slabs = pair_tiles * ((a.k + BK - 1) / BK);
     const bool pair_two_slabs = a.k % (2 * BK) == 0 && !g_one_slab_stages;
-    const bool pair_pays = pair_two_slabs ? (pair_tiles >= 64 && pair_slabs >= 96 * 16) : pair_tiles >= 2 * device_sms();
+    const bool pair_pays = pair_two_slabs ? pair_slabs >= 2LL * device_sms() * 16 : pair_tiles >= 2 * device_sms();
     const bool pair_wanted = g_pair_mode == 1 || (g_pair_mode == 0 && pair_pays);
     if (pair_legal && pair_wanted && g_pair_mode != 2) {
         p.splits = 1;
