@@ -82,6 +82,7 @@ def test_block_quantizer_rejects_bad_shapes(pkg):
         pkg.quantize_blocks128(torch.zeros(16, 128, device=DEV), block_rows=64)
 
 
+@pytest.mark.gpu
 def test_the_library_picks_the_wide_tile_when_it_fills_the_machine(pkg, ref):
     """Unforced: 2048 x 6144 is 384 wide tiles (>= one per SM) -> 256-wide kernel; the same problem forced to 128-wide
     tiles gives the same bits."""
@@ -103,10 +104,6 @@ def test_the_library_picks_the_wide_tile_when_it_fills_the_machine(pkg, ref):
     qw_ref, sw_ref = ref.quantize_blocks128(w)
     want = ref.linear_blocks128(qx_ref, sx_ref, qw_ref, sw_ref, out_dtype=torch.float16)
     assert torch.equal(y_auto.cpu(), want) and torch.equal(y_128.cpu(), want)
-
-
-test_the_library_picks_the_wide_tile_when_it_fills_the_machine = pytest.mark.gpu(
-    test_the_library_picks_the_wide_tile_when_it_fills_the_machine)
 
 
 CASES = [  # m, k, n, out dtype, layout, bias
