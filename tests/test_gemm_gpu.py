@@ -139,6 +139,31 @@ def test_fused_linear_activation(pkg, ref, act):
     assert int(ref.ulp_distance_f16(got16.cpu(), want.to(torch.float16)).max()) <= 2
 
 
+@pytest.mark.parametrize("act", [1, 2])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("pair", [0, 1])
+def test_vector_activation_epilogue_equals_the_guarded_one(pkg, act, out_dtype, pair):
+    """A linear that dequantizes and activates (the MLP's up linear) through the lean kernel's vector epilogue, and
+    the same call with a column-scale vector that is not 16-byte aligned, which takes the general kernel's guarded
+    per-element epilogue.  Same operations in the same order: the two must agree bit for bit."""
+    m, k, n = 512, 1024, 1024
+    g = torch.Generator().manual_seed(12)
+    a, b = codes(m, k, 13).to(DEV), codes(n, k, 14).to(DEV)
+    sx = (torch.rand(m, generator=g) * 0.02 + 0.005).to(DEV)
+    sw_buf = torch.zeros(n + 4, device=DEV)
+    sw_buf[1:n + 1] = (torch.rand(n, generator=g) * 2e-4 + 1e-5).to(DEV)
+    sw_aligned = sw_buf[1:n + 1].clone()
+    pkg.lib().b200_w8a8_set_pair_mma(pair)   # 1: the CTA-pair kernel where it is legal (aligned vectors only)
+    try:
+        fast = pkg.linear(a, sx, b, sw_aligned, act=act, out_dtype=out_dtype)
+        slow = pkg.linear(a, sx, b, sw_buf[1:n + 1], act=act, out_dtype=out_dtype)
+    finally:
+        pkg.lib().b200_w8a8_set_pair_mma(0)
+    torch.cuda.synchronize()
+    assert pkg.poll_status() == 0
+    assert torch.equal(fast.view(torch.uint8), slow.view(torch.uint8))
+
+
 def test_fused_linear_strided_output(pkg, ref):
     """Output written into a column block of a wider buffer (row stride > N)."""
     m, k, n = 256, 256, 512
