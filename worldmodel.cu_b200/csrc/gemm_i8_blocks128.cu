@@ -12,7 +12,8 @@
 // out of tree), so parity here is against this library's own CPU restatement of the rule only.
 //
 // Kernel shape: a 128 x 128 or 128 x 256 output tile per persistent CTA, so a warp's columns see exactly one
-// activation block row and one weight block row and a K block's scale pair is a single number per warp.  The
+// activation block row and one weight block row and a K block's scale pair is a single number per warp (per
+// thread when the activations carry a scale per token row, the 1 x 128 form).  The
 // tensor core writes K block after K block into the accumulators of tensor memory in turn (four of 128 columns
 // or two of 256); eight epilogue warps drain each one as soon as it is complete (`tcgen05.ld` in chunks of 16
 // columns, the next chunk in flight while the current one is folded in; the slot is handed back when the last
