@@ -37,7 +37,7 @@ LINEARS = [("qkv", N_QKV, D_MODEL), ("out", D_MODEL, D_MODEL), ("ctrl", D_MODEL,
 OPS_PER_ROW_LAYER = 2 * sum(n * k for _, n, k in LINEARS)  # 109,051,904
 WEIGHT_BYTES_LAYER = sum(n * k for _, n, k in LINEARS)     # 54,525,952
 # DRAM read+write of the five GEMM launches of one layer from the committed ncu captures (profiles/)
-NCU_DRAM_BYTES_PER_LAYER = {512: 69.6e6, 2048: 129.7e6, 8192: 668.5e6}
+NCU_DRAM_BYTES_PER_LAYER = {512: 69.6e6, 2048: 129.7e6, 8192: 668.5e6, 16384: 1521.6e6}
 WORKLOADS = {
     # name: (rows per GPU, chained steps per bench step, activation dtype, band rows)
     "cfg1": (512, 1, "fp16", 0),
@@ -516,6 +516,8 @@ def main():
         raise SystemExit(f"rank {rank} of {world} has no world to run: use at most {args.worlds} GPUs")
     dtype = torch.float16 if dt_name == "fp16" else torch.bfloat16
     use_graph = not args.no_graph
+    if args.workload == "cfg3" and rows >= 32768:
+        band = 16384  # bands as tall as still leaves every lane one: the CTA-pair GEMMs gain from more tiles per launch
     if args.band >= 0:
         band = args.band
     lanes = args.lanes if args.lanes > 0 else (2 if args.workload == "cfg3" else 1)
